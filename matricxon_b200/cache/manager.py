@@ -12,7 +12,9 @@ caches of different kinds by layer index (app/runtime/mamba_cache.py:21-70). Her
   moves its length after the step (the reference's two-phase write);
 * a group with a window W gives a page back as soon as its last position is
   ``<= length - W``: the next query sits at ``p >= length`` and needs ``j > p - W``,
-  so no later query can see that page; its table entry becomes -1;
+  so no later query can see that page; its table entry becomes -1. A group whose
+  windows keep the first ``keep_first`` positions in sight never gives back the pages
+  that hold them;
 * a finished request gives everything back; freed pages are reused first (LIFO);
 * beside the pages, every request holds one slot of fixed-size state
   (the analogue of the reference's conv/ssm state, mamba_cache.py:63-70), even
@@ -101,9 +103,11 @@ class SlotPool:
 
 @dataclass(frozen=True)
 class GroupRule:
-    """Lifetime rule of a group: ``window`` None keeps every page until the request ends."""
+    """Lifetime rule of a group: ``window`` None keeps every page until the request ends; with a window, the
+    pages that hold any of the first ``keep_first`` positions are kept as well."""
 
     window: int | None
+    keep_first: int = 0
 
 
 @dataclass
@@ -230,8 +234,10 @@ class CacheManager:
         record.fresh_state = False
         for group, table in enumerate(record.tables):
             keep_from = self._first_needed_logical(group, record.length)
+            # pages that hold one of the first tokens a window never loses sight of stay
+            kept_pages = (self.rules[group].keep_first + self.page_size - 1) // self.page_size
             expired = []
-            for logical in range(min(keep_from, len(table))):
+            for logical in range(kept_pages, min(keep_from, len(table))):
                 if table[logical] >= 0:
                     expired.append(table[logical])
                     table[logical] = -1

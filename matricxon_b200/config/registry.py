@@ -109,6 +109,14 @@ def _register_builtin() -> None:
         config_class=ParunexConfig,
         build_model=_build_decoder,
     ))
+    from matricxon_b200.config.bafusun import BafusunConfig
+
+    register_architecture(ArchitectureEntry(
+        name="Bafusun",
+        aliases=("bafusun",),
+        config_class=BafusunConfig,
+        build_model=_build_decoder,
+    ))
 
 
 _register_builtin()

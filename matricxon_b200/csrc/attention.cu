@@ -2,7 +2,9 @@
 //
 // Visibility rule (the reference's windowed decode attention, app/native/src/mx_attention.c:36-39,
 // and its masks, app/architectures/qwen_layers.py:12-17, app/architectures/gemma4_layers.py:17-34):
-// the query at absolute position p sees key j iff j <= p and (window == 0 or j > p - window).
+// the query at absolute position p sees key j iff j <= p and (window == 0 or j > p - window or j < keep_first):
+// a window may keep the sequence's first `keep_first` tokens in sight for good (0: none); they keep their
+// true positions, and the chunks between them and the window are skipped, not masked.
 // Scores are q.k * scale, softmax is max-subtracted, query head h reads KV head h / (heads / kv heads)
 // (app/native/src/mx_attention.c:16-68). Scores, softmax and the weighted sum are float whatever T is.
 //
@@ -42,6 +44,7 @@ struct AttnParams {
     float scale;
     float softcap;            // > 0: scores become softcap * tanh(score / softcap) before the softmax
     const float* sink;        // [n_heads] or null: exp(sink[h]) joins the softmax's denominator, with no value
+    int keep_first;           // with a window: keys j < keep_first stay visible whatever the distance
 };
 
 template <typename T> struct Vec16;  // 16 bytes of T
@@ -108,11 +111,15 @@ paged_attention_kernel(const AttnParams p) {
     const int pos = p.positions[t];
     const int hi = pos;
     const int lo = (p.window > 0) ? max(0, pos - p.window + 1) : 0;
+    // keys [0, kept) are seen beside [lo, hi]; their chunks that lie wholly before the window's first chunk are
+    // walked first: the walk counts v = 0 .. n_chunks - 1, chunk v for v < n_kept, else first_chunk + v - n_kept
+    const int kept = lo > 0 ? min(p.keep_first, lo) : 0;
     const int first_chunk = lo / KEYS, last_chunk = hi / KEYS;
-    const int n_chunks = last_chunk - first_chunk + 1;
+    const int n_kept = min((kept + KEYS - 1) / KEYS, first_chunk);
+    const int n_chunks = n_kept + last_chunk - first_chunk + 1;
     const int per_split = (n_chunks + p.n_splits - 1) / p.n_splits;
-    const int c_begin = first_chunk + split * per_split;
-    const int c_end = min(last_chunk + 1, c_begin + per_split);
+    const int c_begin = split * per_split;
+    const int c_end = min(n_chunks, c_begin + per_split);
 
     const T* qrow = reinterpret_cast<const T*>(p.q) + (size_t)t * p.q_stride + (size_t)head0 * hd;
     for (int i = tid; i < gc * hd; i += ATT_THREADS) q_s[i] = to_float(qrow[i]);
@@ -130,14 +137,14 @@ paged_attention_kernel(const AttnParams p) {
     const T* cache = reinterpret_cast<const T*>(p.cache);
     const size_t head_stride = (size_t)p.page_size * hd;
 
-    for (int ci = c_begin; ci < c_end; ++ci) {
-        const int c0 = ci * KEYS;
+    for (int vi = c_begin; vi < c_end; ++vi) {
+        const int c0 = (vi < n_kept ? vi : first_chunk + vi - n_kept) * KEYS;
         // ---- stage the chunk's K rows (zero for keys outside [lo, hi])
         for (int item = tid; item < KEYS * cpr; item += ATT_THREADS) {
             const int j = item / cpr, c = item - j * cpr;
             const int kpos = c0 + j;
             uint4 kv = make_uint4(0, 0, 0, 0);
-            if (kpos >= lo && kpos <= hi) {
+            if ((kpos >= lo || kpos < kept) && kpos <= hi) {
                 const int lp = kpos / p.page_size;
                 const long long page = (lp < p.bt_stride) ? bt[lp] : -1;
                 if (page < 0 || page >= p.n_pages) {
@@ -159,7 +166,7 @@ paged_attention_kernel(const AttnParams p) {
                 const int d = item / GROUPS, jg = item - d * GROUPS;
                 const int kpos0 = c0 + jg * E;
                 uint4 raw = make_uint4(0, 0, 0, 0);
-                if (kpos0 <= hi && kpos0 + E - 1 >= lo) {
+                if (kpos0 <= hi && (kpos0 + E - 1 >= lo || kpos0 < kept)) {
                     const int lp = kpos0 / p.page_size;
                     const long long page = (lp < p.bt_stride) ? bt[lp] : -1;
                     if (page >= 0 && page < p.n_pages) {
@@ -174,7 +181,7 @@ paged_attention_kernel(const AttnParams p) {
                 for (int e = 0; e < E; ++e) {
                     const int kpos = kpos0 + e;
                     v_t[(size_t)(jg * E + e) * hd + d] =
-                        (kpos >= lo && kpos <= hi) ? elems[e] : from_float<T>(0.f);
+                        ((kpos >= lo || kpos < kept) && kpos <= hi) ? elems[e] : from_float<T>(0.f);
                 }
             }
         }
@@ -183,7 +190,7 @@ paged_attention_kernel(const AttnParams p) {
         // ---- scores: lane = key, this warp's heads are warp, warp + 4, ...
         {
             const int kpos = c0 + lane;
-            const bool valid = (kpos >= lo && kpos <= hi);
+            const bool valid = ((kpos >= lo || kpos < kept) && kpos <= hi);
             float s[HEADS_PER_WARP];
 #pragma unroll
             for (int hs = 0; hs < HEADS_PER_WARP; ++hs) s[hs] = 0.f;
@@ -480,7 +487,7 @@ extern "C" int mx_paged_attention(const void* q, int dtype, int q_stride, const 
                                   int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                   int window, float scale, void* out, int out_stride,
                                   int n_splits, float* scratch, int* status, float softcap, const float* sink,
-                                  cudaStream_t stream) {
+                                  int keep_first, cudaStream_t stream) {
     if (n_tokens <= 0) return MX_OK;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         MX_REFUSE("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
@@ -500,6 +507,7 @@ extern "C" int mx_paged_attention(const void* q, int dtype, int q_stride, const 
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.page_size = page_size;
     p.window = window; p.n_splits = n_splits; p.scale = scale;
     p.softcap = softcap; p.sink = sink;
+    p.keep_first = window > 0 ? max(keep_first, 0) : 0;
     const bool two = head_dim > ATT_THREADS;
     if (dtype == MX_DTYPE_F32)
         return two ? launch_attention<float, 2>(p, n_tokens, stream) : launch_attention<float, 1>(p, n_tokens, stream);
@@ -590,5 +598,5 @@ extern "C" int mx_paged_attention_static(const void* q, int dtype, int q_stride,
     if (rc != MX_OK) return rc;
     return mx_paged_attention(q, dtype, q_stride, cache, n_pages, page_size, block_tables, bt_stride,
                               tok_seq, positions, n_tokens, n_heads, n_kv_heads, head_dim, window,
-                              scale, out, out_stride, n_splits, scratch, status, 0.f, nullptr, stream);
+                              scale, out, out_stride, n_splits, scratch, status, 0.f, nullptr, 0, stream);
 }

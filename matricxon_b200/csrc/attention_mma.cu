@@ -1,7 +1,7 @@
 // Tensor-core paged attention for bfloat16: prompt portions and decode tokens.
 //
 // Same mathematics and visibility rule as attention.cu (query at p sees key j iff j <= p and
-// (window == 0 or j > p - window); scores q.k * scale; float softmax; query head h reads KV
+// (window == 0 or j > p - window or j < keep_first); scores q.k * scale; float softmax; query head h reads KV
 // head h / group), cf. app/native/src/mx_attention.c:16-68 and
 // app/architectures/qwen_layers.py:12-17,94-100.
 //
@@ -11,7 +11,9 @@
 // same causal limit and every key they load is used by all of them.
 //
 // Work. A block (four warps for wide tiles, eight for narrow ones) owns a tile of rows of one (sequence, KV head) and a split of
-// the keys, walked in chunks of 32 absolute positions. A page's keys for one KV head are one
+// the keys, walked in chunks of 32 absolute positions (under a window that keeps the sequence's first
+// tokens in sight: first the chunks that hold those, then the window's; the walk counts both in one row
+// of "virtual" chunks and `chunk_of` says which chunk of positions a count stands for). A page's keys for one KV head are one
 // contiguous piece of memory and so are its values, so a chunk reaches shared memory as a
 // few bulk asynchronous copies (cp.async.bulk, completion counted on an mbarrier) issued by
 // one thread, several chunks ahead of the arithmetic. Pages must hold 8, 16 or 32 slots.
@@ -64,6 +66,7 @@ struct MmaAttnParams {
     long long n_pages;
     int n_tiles, q_stride, out_stride, bt_stride;
     int n_heads, n_kv_heads, page_size, page_shift, window, n_splits;
+    int keep_first;              // with a window: keys j < keep_first stay visible whatever the distance
     float scale_log2;            // scale * log2(e)
     // capped scores: cap_log2 = cap * log2(e) > 0 turns score * scale into cap * tanh(score * scale / cap)
     // (cap_in = scale / cap), already in the units of the exponential; 0: no cap
@@ -129,11 +132,11 @@ __device__ __forceinline__ void bulk_copy(void* smem_dst, const void* gmem_src, 
 
 // Brings the chunk starting at key c0 into a stage: keys as [key][HD], values page by page as
 // [HD][page_size]. `who` of `n_who` cooperating threads; thread 0 issues the copies. Pages the
-// request no longer holds (they lie wholly outside [lo, hi]) are filled with zeros instead.
+// request no longer holds (they lie wholly outside [lo, hi] and [0, kept)) are filled with zeros instead.
 template <int HD>
 __device__ __forceinline__ void issue_chunk(const MmaAttnParams& p, __nv_bfloat16* ks,
                                             __nv_bfloat16* vs, unsigned long long* bar, int c0, int lo,
-                                            int hi, const int* bt, const __nv_bfloat16* kbase,
+                                            int hi, int kept, const int* bt, const __nv_bfloat16* kbase,
                                             const __nv_bfloat16* vbase, size_t page_stride, int who,
                                             int n_who, const int* cached = nullptr) {
     const int ps = p.page_size;
@@ -146,7 +149,7 @@ __device__ __forceinline__ void issue_chunk(const MmaAttnParams& p, __nv_bfloat1
         page_of[pg] = -1;
         if (pg < pages) {
             const int key0 = c0 + pg * ps;
-            if (key0 <= hi && key0 + ps - 1 >= lo) {
+            if (key0 <= hi && (key0 + ps - 1 >= lo || key0 < kept)) {
                 const int lp = key0 >> p.page_shift;
                 // `cached`: this chunk's block-table entries, read ahead into shared memory
                 const long long page = cached != nullptr ? cached[pg] : (lp < p.bt_stride ? bt[lp] : -1);
@@ -249,11 +252,16 @@ attention_mma_kernel(const MmaAttnParams p) {
     const int all_hi = warp_has_rows ? ctx + row0 / group : -1;
     const int all_lo = p.window > 0 ? max(0, hi_warp - p.window + 1) : 0;
     const bool rows_full = row0 + 15 < n_rows;
+    // keys [0, kept) are seen beside the window's: their chunks that lie wholly before the window's first one
+    // are walked first. The walk counts v = 0 .. n_chunks - 1: chunk v for v < n_kept, then the window's chunks.
+    const int kept = lo_tile > 0 ? min(p.keep_first, lo_tile) : 0;
     const int first_chunk = lo_tile / CHUNK, last_chunk = hi_tile / CHUNK;
-    const int n_chunks = last_chunk - first_chunk + 1;
+    const int n_kept = min((kept + CHUNK - 1) / CHUNK, first_chunk);
+    const int n_chunks = n_kept + last_chunk - first_chunk + 1;
     const int per_split = (n_chunks + p.n_splits - 1) / p.n_splits;
-    const int c_begin = first_chunk + split * per_split;
-    const int c_end = min(last_chunk + 1, c_begin + per_split);
+    const int c_begin = split * per_split;
+    const int c_end = min(n_chunks, c_begin + per_split);
+    auto chunk_of = [&](int v) { return v < n_kept ? v : first_chunk + v - n_kept; };
 
     const int* bt = p.block_tables + (size_t)seq * p.bt_stride;
     const size_t head_stride = (size_t)p.page_size * HD;
@@ -272,13 +280,13 @@ attention_mma_kernel(const MmaAttnParams p) {
     // kept are looked up in global memory).
     auto cached_for = [&](int i) -> const int* {
         const int pages = CHUNK >> p.page_shift;
-        const int first = (my_first + NARROW_WARPS * i) * pages;
+        const int first = chunk_of(my_first + NARROW_WARPS * i) * pages;
         return first + pages <= min(p.bt_stride, NARROW_TABLE) ? narrow_table + first : nullptr;
     };
-    const bool first_is_old = (my_first + 1) * CHUNK <= ctx;
+    const bool first_is_old = (chunk_of(my_first) + 1) * CHUNK <= ctx;
     if (NARROW && my_count > 0 && first_is_old)
-        issue_chunk<HD>(p, my_stages, my_stages + CHUNK * HD, &my_bars[0], my_first * CHUNK, lo_tile,
-                        hi_tile, bt, kbase, vbase, page_stride, lane, 32, cached_for(0));
+        issue_chunk<HD>(p, my_stages, my_stages + CHUNK * HD, &my_bars[0], chunk_of(my_first) * CHUNK, lo_tile,
+                        hi_tile, kept, bt, kbase, vbase, page_stride, lane, 32, cached_for(0));
     // queries and the newest keys and values come from the kernels before this one
     pdl_wait();
     // Q fragments: 16 bytes of each owned row per 32-wide block. A row beyond the tile reads the
@@ -300,8 +308,9 @@ attention_mma_kernel(const MmaAttnParams p) {
 
     // ---- arithmetic on one chunk, or on two consecutive chunks with one softmax update for both
     auto compute = [&](auto n_chunks_tag, const __nv_bfloat16* ks0, const __nv_bfloat16* vs0,
-                       const __nv_bfloat16* ks1, const __nv_bfloat16* vs1, int c0) {
+                       const __nv_bfloat16* ks1, const __nv_bfloat16* vs1, int c0, int c1) {
         constexpr int NCH = decltype(n_chunks_tag)::value;
+        const int first_key[2] = {c0, c1};         // of each chunk; c1 >= c0 + CHUNK with two chunks
         const __nv_bfloat16* ksv[2] = {ks0, ks1};
         const __nv_bfloat16* vsv[2] = {vs0, vs1};
         // scores: block b of a chunk gives this thread that chunk's keys 8t + 2b, 8t + 2b + 1.
@@ -360,7 +369,7 @@ attention_mma_kernel(const MmaAttnParams p) {
         }
         // mask (only where the chunks cross an edge), running max and sum for rows g, g + 8
         float m_new[2] = {m_run[0], m_run[1]};
-        const bool plain = rows_full && c0 >= all_lo && c0 + NCH * CHUNK - 1 <= all_hi;
+        const bool plain = rows_full && c0 >= all_lo && first_key[NCH - 1] + CHUNK - 1 <= all_hi;
         // scores stay unscaled until the exponential: exp2(s * c - m * c) is one FMA and one ex2
         // (c > 0, so the maximum of s * c is c times the maximum of s)
         float raw_max[2] = {-INFINITY, -INFINITY};
@@ -379,8 +388,8 @@ attention_mma_kernel(const MmaAttnParams p) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int i = e >> 1;
-                        const int key = c0 + CHUNK * ch + 8 * t + 2 * b + (e & 1);
-                        const bool visible = r_valid[i] && key <= r_pos[i] && key >= r_lo[i];
+                        const int key = first_key[ch] + 8 * t + 2 * b + (e & 1);
+                        const bool visible = r_valid[i] && key <= r_pos[i] && (key >= r_lo[i] || key < p.keep_first);
                         s[ch][b][e] = visible ? s[ch][b][e] : -INFINITY;
                         raw_max[i] = fmaxf(raw_max[i], s[ch][b][e]);
                     }
@@ -437,7 +446,7 @@ attention_mma_kernel(const MmaAttnParams p) {
                 o[nb][2] *= alpha[1]; o[nb][3] *= alpha[1];
             }
         }
-        if (c0 + NCH * CHUNK - 1 <= hi_tile) {
+        if (first_key[NCH - 1] + CHUNK - 1 <= hi_tile) {
 #pragma unroll
             for (int nb0 = 0; nb0 < NB; nb0 += 4)
 #pragma unroll
@@ -458,7 +467,7 @@ attention_mma_kernel(const MmaAttnParams p) {
             unsigned keep[NCH][4];
 #pragma unroll
             for (int ch = 0; ch < NCH; ++ch) {
-                const int vkey0 = c0 + CHUNK * ch + 8 * t;
+                const int vkey0 = first_key[ch] + 8 * t;
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                     const bool lo_ok = vkey0 + 2 * w <= hi_tile, hi_ok = vkey0 + 2 * w + 1 <= hi_tile;
@@ -481,24 +490,27 @@ attention_mma_kernel(const MmaAttnParams p) {
         // warps a block has eight chunks in flight, and a warp fetches its next chunk when it is done with
         // the one before (more warps hide the copies' latency better than deeper per-warp pipelines did)
         if (my_count > 0 && !first_is_old)
-            issue_chunk<HD>(p, my_stages, my_stages + CHUNK * HD, &my_bars[0], my_first * CHUNK, lo_tile,
-                            hi_tile, bt, kbase, vbase, page_stride, lane, 32, cached_for(0));
+            issue_chunk<HD>(p, my_stages, my_stages + CHUNK * HD, &my_bars[0], chunk_of(my_first) * CHUNK, lo_tile,
+                            hi_tile, kept, bt, kbase, vbase, page_stride, lane, 32, cached_for(0));
         for (int i = 0; i < my_count; ++i) {
             const int st = i % NARROW_STAGES;
             if (NARROW_STAGES > 1 && i + 1 < my_count) {
                 const int nx = (i + 1) % NARROW_STAGES;
                 __nv_bfloat16* ks = my_stages + (size_t)nx * STAGE_ELEMS;
-                issue_chunk<HD>(p, ks, ks + CHUNK * HD, &my_bars[nx], (my_first + NARROW_WARPS * (i + 1)) * CHUNK,
-                                lo_tile, hi_tile, bt, kbase, vbase, page_stride, lane, 32, cached_for(i + 1));
+                issue_chunk<HD>(p, ks, ks + CHUNK * HD, &my_bars[nx], chunk_of(my_first + NARROW_WARPS * (i + 1)) * CHUNK,
+                                lo_tile, hi_tile, kept, bt, kbase, vbase, page_stride, lane, 32, cached_for(i + 1));
             }
             __syncwarp();
             mbar_wait(&my_bars[st], (unsigned)((i / NARROW_STAGES) & 1), p.status);
             const __nv_bfloat16* ks = my_stages + (size_t)st * STAGE_ELEMS;
-            compute(One{}, ks, ks + CHUNK * HD, ks, ks + CHUNK * HD, (my_first + NARROW_WARPS * i) * CHUNK);
+            {
+                const int c0 = chunk_of(my_first + NARROW_WARPS * i) * CHUNK;
+                compute(One{}, ks, ks + CHUNK * HD, ks, ks + CHUNK * HD, c0, c0);
+            }
             __syncwarp();                         // the stage may be refilled from here on
             if (NARROW_STAGES == 1 && i + 1 < my_count)
                 issue_chunk<HD>(p, my_stages, my_stages + CHUNK * HD, &my_bars[0],
-                                (my_first + NARROW_WARPS * (i + 1)) * CHUNK, lo_tile, hi_tile, bt, kbase, vbase,
+                                chunk_of(my_first + NARROW_WARPS * (i + 1)) * CHUNK, lo_tile, hi_tile, kept, bt, kbase, vbase,
                                 page_stride, lane, 32, cached_for(i + 1));
         }
         // ---- combine the warps' partial results through shared memory (stages are free)
@@ -577,8 +589,8 @@ attention_mma_kernel(const MmaAttnParams p) {
     auto issue_wide = [&](int ci) {
         if (ci < c_end) {
             __nv_bfloat16* ks = stages + (size_t)((ci - c_begin) % WIDE_STAGES) * STAGE_ELEMS;
-            issue_chunk<HD>(p, ks, ks + CHUNK * HD, &bars[(ci - c_begin) % WIDE_STAGES], ci * CHUNK, lo_tile,
-                            hi_tile, bt, kbase, vbase, page_stride, tid, MMA_THREADS);
+            issue_chunk<HD>(p, ks, ks + CHUNK * HD, &bars[(ci - c_begin) % WIDE_STAGES], chunk_of(ci) * CHUNK, lo_tile,
+                            hi_tile, kept, bt, kbase, vbase, page_stride, tid, MMA_THREADS);
         }
     };
     issue_wide(c_begin);
@@ -588,19 +600,19 @@ attention_mma_kernel(const MmaAttnParams p) {
         __syncthreads();                         // every warp is done with the pair before: its stages are free
         issue_wide(ci + 2);
         issue_wide(ci + 3);
-        const int c0 = ci * CHUNK;
+        // the chunks of a pair need not be neighbours: the last of the kept first tokens and the window's first
         const bool two = ci + 1 < c_end;
-        const int span = two ? 2 * CHUNK : CHUNK;
-        if (!(warp_has_rows && c0 <= hi_warp && c0 + span - 1 >= lo_warp)) continue;
+        const int c0 = chunk_of(ci) * CHUNK, c1 = two ? chunk_of(ci + 1) * CHUNK : c0;
+        if (!(warp_has_rows && c0 <= hi_warp && (c1 + CHUNK - 1 >= lo_warp || c0 < kept))) continue;
         const int st0 = i % WIDE_STAGES, st1 = (i + 1) % WIDE_STAGES;
         const __nv_bfloat16* ks0 = stages + (size_t)st0 * STAGE_ELEMS;
         const __nv_bfloat16* ks1 = stages + (size_t)st1 * STAGE_ELEMS;
         mbar_wait(&bars[st0], (unsigned)((i / WIDE_STAGES) & 1), p.status);
         if (two) {
             mbar_wait(&bars[st1], (unsigned)(((i + 1) / WIDE_STAGES) & 1), p.status);
-            compute(Two{}, ks0, ks0 + CHUNK * HD, ks1, ks1 + CHUNK * HD, c0);
+            compute(Two{}, ks0, ks0 + CHUNK * HD, ks1, ks1 + CHUNK * HD, c0, c1);
         } else {
-            compute(One{}, ks0, ks0 + CHUNK * HD, ks0, ks0 + CHUNK * HD, c0);
+            compute(One{}, ks0, ks0 + CHUNK * HD, ks0, ks0 + CHUNK * HD, c0, c0);
         }
     }
 
@@ -671,7 +683,7 @@ extern "C" int mx_paged_attention_mma(const void* q, int q_stride, const void* c
                                       int n_heads, int n_kv_heads, int head_dim, int window,
                                       float scale, void* out, int out_stride, int n_splits,
                                       float* scratch, int* status, float softcap, const float* sink,
-                                      cudaStream_t stream) {
+                                      int keep_first, cudaStream_t stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return MX_OK;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         MX_REFUSE("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
@@ -693,6 +705,7 @@ extern "C" int mx_paged_attention_mma(const void* q, int q_stride, const void* c
     p.out_stride = out_stride; p.bt_stride = bt_stride; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
     p.page_size = page_size; p.page_shift = page_size == 8 ? 3 : (page_size == 16 ? 4 : 5);
     p.window = window; p.n_splits = n_splits;
+    p.keep_first = window > 0 ? max(keep_first, 0) : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     p.cap_in = softcap > 0.f ? scale / softcap : 0.f;

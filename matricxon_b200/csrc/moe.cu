@@ -7,6 +7,11 @@
 //   The kernel also counts the pairs of every expert and gives each (token, slot) pair its place among its
 //   expert's pairs (the order inside an expert is whatever the atomics make it: every row of a grouped product
 //   depends on that row alone, so the order changes no number).
+// mx_moe_route_softmax: the same outputs from another rule. The router has `n_experts + n_identity` rows; the scores
+//   are the softmax over all of them; the choice ranks score + correction[e] (a float per row, optional) and takes the
+//   `top` largest (ties to the lower index); the weights are the winners' plain scores over their sum (+ 1e-20). The
+//   last `n_identity` rows stand for experts without matrices that return their input: such a pair keeps its id
+//   (>= n_experts), is counted nowhere and gets no sorted row; the combine kernels add weight * input for it.
 // mx_moe_plan (one block): from the counts, the first sorted row of every expert and the list of row tiles
 //   (expert, first sorted row, rows) that the grouped products walk; the number of tiles stays on the device.
 // mx_moe_scatter: order[first[e] + place] = pair: the pairs sorted by expert.
@@ -37,21 +42,16 @@ __device__ __forceinline__ void arg_best(float& v, int& i) {
     }
 }
 
+// z[e] = router[e] . h for every router row, in float: the token's activations staged in shared memory (h_s [K]),
+// a warp per row. Ends with a barrier: every thread may read z afterwards.
 template <typename T>
-__global__ void __launch_bounds__(256)
-moe_route_kernel(const T* __restrict__ h, int ld, const float* __restrict__ router, int K, int n_experts, int top,
-                 int n_groups, int keep, float scale, int* __restrict__ ids, float* __restrict__ weights,
-                 int* __restrict__ counts, int* __restrict__ place) {
-    extern __shared__ __align__(16) float route_s[];
-    float* h_s = route_s;                         // [K]
-    float* score = h_s + K;                       // [experts]
-    float* open = score + n_experts;              // [experts]: the score while the expert may still be chosen, else -1
-    float* worth = open + n_experts;              // [groups]
-    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int k = tid; k < K; k += blockDim.x) h_s[k] = to_float(h[(size_t)t * ld + k]);
+__device__ __forceinline__ void router_logits(const T* __restrict__ h, const float* __restrict__ router, int K,
+                                              int n_rows, float* h_s, float* z_out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int k = tid; k < K; k += blockDim.x) h_s[k] = to_float(h[k]);
     __syncthreads();
     const bool vec = K % 4 == 0 && (reinterpret_cast<uintptr_t>(router) & 15) == 0;
-    for (int e = warp; e < n_experts; e += blockDim.x >> 5) {
+    for (int e = warp; e < n_rows; e += blockDim.x >> 5) {
         const float* w = router + (size_t)e * K;
         float z = 0.f;
         if (vec) {
@@ -81,8 +81,24 @@ moe_route_kernel(const T* __restrict__ h, int ld, const float* __restrict__ rout
             for (int k = lane; k < K; k += 32) z = fmaf(w[k], h_s[k], z);
         }
         z = warp_sum(z);
-        if (lane == 0) score[e] = 1.0f / (1.0f + expf(-z));
+        if (lane == 0) z_out[e] = z;
     }
+    __syncthreads();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const T* __restrict__ h, int ld, const float* __restrict__ router, int K, int n_experts, int top,
+                 int n_groups, int keep, float scale, int* __restrict__ ids, float* __restrict__ weights,
+                 int* __restrict__ counts, int* __restrict__ place) {
+    extern __shared__ __align__(16) float route_s[];
+    float* h_s = route_s;                         // [K]
+    float* score = h_s + K;                       // [experts]
+    float* open = score + n_experts;              // [experts]: the score while the expert may still be chosen, else -1
+    float* worth = open + n_experts;              // [groups]
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    router_logits(h + (size_t)t * ld, router, K, n_experts, h_s, score);
+    for (int e = tid; e < n_experts; e += blockDim.x) score[e] = 1.0f / (1.0f + expf(-score[e]));
     __syncthreads();
     if (warp != 0) return;
     const int per = n_experts / n_groups;
@@ -140,6 +156,59 @@ moe_route_kernel(const T* __restrict__ h, int ld, const float* __restrict__ rout
         for (int slot = 32; slot < top; ++slot) weights[(size_t)t * top + slot] *= norm;
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_route_softmax_kernel(const T* __restrict__ h, int ld, const float* __restrict__ router, int K, int n_experts,
+                         int n_identity, int top, const float* __restrict__ correction, int* __restrict__ ids,
+                         float* __restrict__ weights, int* __restrict__ counts, int* __restrict__ place) {
+    extern __shared__ __align__(16) float route_s[];
+    const int n_rows = n_experts + n_identity;
+    float* h_s = route_s;                         // [K]
+    float* score = h_s + K;                       // [rows]: logits, then softmax scores
+    float* open = score + n_rows;                 // [rows]: score + correction while the row may still be chosen
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    router_logits(h + (size_t)t * ld, router, K, n_rows, h_s, score);
+    if (threadIdx.x >= 32) return;
+    float m = -INFINITY;
+    for (int e = lane; e < n_rows; e += 32) m = fmaxf(m, score[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < n_rows; e += 32) {
+        const float v = expf(score[e] - m);
+        score[e] = v;
+        sum += v;
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < n_rows; e += 32) {
+        const float sc = score[e] / sum;
+        score[e] = sc;
+        open[e] = sc + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    float total = 0.f;
+    for (int slot = 0; slot < top; ++slot) {
+        float v = -INFINITY;
+        int i = 0x7fffffff;
+        for (int e = lane; e < n_rows; e += 32)
+            if (open[e] > v) { v = open[e]; i = e; }
+        arg_best(v, i);
+        if (i >= n_rows) i = 0;                   // nothing comparable left (scores that are no numbers)
+        __syncwarp();
+        const float sc = score[i];
+        if (lane == 0) {
+            open[i] = -INFINITY;
+            ids[(size_t)t * top + slot] = i;
+            weights[(size_t)t * top + slot] = sc;  // normalised below
+            place[(size_t)t * top + slot] = i < n_experts ? atomicAdd(&counts[i], 1) : 0;
+        }
+        __syncwarp();
+        total += sc;
+    }
+    const float norm = 1.f / (total + 1e-20f);
+    __syncwarp();
+    for (int slot = lane; slot < top; slot += 32) weights[(size_t)t * top + slot] *= norm;
+}
+
 __global__ void moe_plan_kernel(const int* __restrict__ counts, int n_experts, int tile_rows, int* __restrict__ first,
                                 int* __restrict__ tile_map, int* __restrict__ n_tiles) {
     extern __shared__ int plan_s[];               // [experts + 1]: first tile of every expert
@@ -167,19 +236,32 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int n_experts, i
 }
 
 __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ place,
-                                   const int* __restrict__ first, int* __restrict__ order, int n_pairs) {
+                                   const int* __restrict__ first, int* __restrict__ order, int n_pairs,
+                                   int n_experts) {
     const int p = blockIdx.x * blockDim.x + threadIdx.x;
-    if (p < n_pairs) order[first[ids[p]] + place[p]] = p;
+    // a pair of an expert without matrices (id >= n_experts) has no sorted row
+    if (p < n_pairs && ids[p] < n_experts) order[first[ids[p]] + place[p]] = p;
 }
 
 __device__ __forceinline__ float act_silu(float g) { return g / (1.0f + expf(-g)); }
 
-// ACT: 0 = gelu (tanh form), 1 = silu
+// the gate capped from above, the linear branch from both sides (limit <= 0: neither), a sigmoid of a slope, a shift
+struct ClampedAct { float limit, slope, shift; };
+__device__ __forceinline__ float act_clamped(float g, float u, const ClampedAct& c) {
+    if (c.limit > 0.f) {
+        g = fminf(g, c.limit);
+        u = fminf(fmaxf(u, -c.limit), c.limit);
+    }
+    return g / (1.0f + expf(-c.slope * g)) * (u + c.shift);
+}
+
+// ACT: 0 = gelu (tanh form), 1 = silu, 2 = clamped (ClampedAct)
 template <typename T, bool GLU, int ACT>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ a, int lda, const int* __restrict__ order, int a_div, const T* __restrict__ w,
                 long long expert_stride, int N, int K, const int* __restrict__ tile_map,
-                const int* __restrict__ n_tiles, void* __restrict__ out_raw, const float* __restrict__ pair_weight) {
+                const int* __restrict__ n_tiles, void* __restrict__ out_raw, const float* __restrict__ pair_weight,
+                const ClampedAct clamped) {
     if ((int)blockIdx.y >= n_tiles[0]) return;
     __shared__ float a_s[MOE_BK][MOE_BM + 1], w_s[MOE_BK][MOE_BN + 1], u_s[GLU ? MOE_BK : 1][MOE_BN + 1];
     __shared__ int src_row[MOE_BM];
@@ -237,8 +319,9 @@ moe_gemm_kernel(const T* __restrict__ a, int lda, const int* __restrict__ order,
             if (n >= N) continue;
             if (GLU) {
                 const float g = acc[r][c];
-                const float act = ACT == 0 ? gelu_tanh(g) : act_silu(g);
-                reinterpret_cast<T*>(out_raw)[(size_t)(row0 + row) * N + n] = from_float<T>(act * acc_u[r][c]);
+                const float value = ACT == 2 ? act_clamped(g, acc_u[r][c], clamped)
+                                             : (ACT == 0 ? gelu_tanh(g) : act_silu(g)) * acc_u[r][c];
+                reinterpret_cast<T*>(out_raw)[(size_t)(row0 + row) * N + n] = from_float<T>(value);
             } else {
                 const int pair = order[row0 + row];
                 reinterpret_cast<float*>(out_raw)[(size_t)pair * N + n] = acc[r][c] * pair_weight[pair];
@@ -247,14 +330,22 @@ moe_gemm_kernel(const T* __restrict__ a, int lda, const int* __restrict__ order,
     }
 }
 
+// `ids` / `input` (both or neither): a pair whose id is >= n_experts belongs to an expert that returns its input;
+// nobody wrote its row, and weight[pair] * input[t] stands for it (input in float or bfloat16)
+template <typename TIn>
 __global__ void moe_combine_kernel(const float* __restrict__ pairs, float* __restrict__ residual, int top, int width,
-                                   long long count) {
+                                   long long count, const int* __restrict__ ids, const float* __restrict__ weight,
+                                   const TIn* __restrict__ input, int input_ld, int n_experts) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
     const long long t = i / width;
     const int c = (int)(i - t * width);
     float sum = 0.f;
-    for (int s = 0; s < top; ++s) sum += pairs[((size_t)t * top + s) * width + c];
+    for (int s = 0; s < top; ++s) {
+        const long long pair = t * top + s;
+        if (ids && ids[pair] >= n_experts) sum += weight[pair] * to_float(input[(size_t)t * input_ld + c]);
+        else sum += pairs[(size_t)pair * width + c];
+    }
     residual[i] += sum;
 }
 
@@ -270,10 +361,12 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ h, int ld, c
 }
 
 // residual[t] += sum over the token's pairs of weight[pair] * rows[place of the pair among the sorted rows]
+template <typename TIn>
 __global__ void moe_combine_sorted_kernel(const float* __restrict__ rows, const int* __restrict__ ids,
                                           const int* __restrict__ place, const int* __restrict__ first,
                                           const float* __restrict__ weight, float* __restrict__ residual, int top,
-                                          int width, long long count) {
+                                          int width, long long count, const TIn* __restrict__ input, int input_ld,
+                                          int n_experts) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
     const long long t = i / width;
@@ -281,16 +374,28 @@ __global__ void moe_combine_sorted_kernel(const float* __restrict__ rows, const 
     float sum = 0.f;
     for (int s = 0; s < top; ++s) {
         const long long pair = t * top + s;
-        sum += weight[pair] * rows[((size_t)first[ids[pair]] + place[pair]) * width + c];
+        const int e = ids[pair];
+        if (e >= n_experts) sum += weight[pair] * to_float(input[(size_t)t * input_ld + c]);
+        else sum += weight[pair] * rows[((size_t)first[e] + place[pair]) * width + c];
     }
     residual[i] += sum;
 }
 
 // the same, four columns a thread (width a multiple of 4, 16-byte aligned rows)
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename TIn>
 __global__ void moe_combine_sorted_vec_kernel(const float* __restrict__ rows, const int* __restrict__ ids,
                                               const int* __restrict__ place, const int* __restrict__ first,
                                               const float* __restrict__ weight, float* __restrict__ residual, int top,
-                                              int width4, long long count) {
+                                              int width4, long long count, const TIn* __restrict__ input,
+                                              int input_ld, int n_experts) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
     const long long t = i / width4;
@@ -299,7 +404,9 @@ __global__ void moe_combine_sorted_vec_kernel(const float* __restrict__ rows, co
     for (int s = 0; s < top; ++s) {
         const long long pair = t * top + s;
         const float w = weight[pair];
-        const float4 v = reinterpret_cast<const float4*>(rows)[((size_t)first[ids[pair]] + place[pair]) * width4 + c];
+        const int e = ids[pair];
+        const float4 v = e >= n_experts ? load4(input + (size_t)t * input_ld + 4 * (size_t)c)
+                                        : reinterpret_cast<const float4*>(rows)[((size_t)first[e] + place[pair]) * width4 + c];
         sum.x = fmaf(w, v.x, sum.x); sum.y = fmaf(w, v.y, sum.y); sum.z = fmaf(w, v.z, sum.z); sum.w = fmaf(w, v.w, sum.w);
     }
     reinterpret_cast<float4*>(residual)[i] = sum;
@@ -361,6 +468,25 @@ extern "C" int mx_moe_route(const void* h, int dtype, int ld, const float* route
     return mx_launch_status();
 }
 
+extern "C" int mx_moe_route_softmax(const void* h, int dtype, int ld, const float* router, int K, int n_experts,
+                                    int n_identity, int top, const float* correction, int* ids, float* weights,
+                                    int* counts, int* place, int n_tokens, cudaStream_t stream) {
+    if (n_tokens <= 0) return MX_OK;
+    const int n_rows = n_experts + n_identity;
+    if (n_experts < 0 || n_identity < 0 || top <= 0 || top > n_rows)
+        MX_REFUSE("router: top %d of %d experts and %d without matrices", top, n_experts, n_identity);
+    const size_t smem = ((size_t)K + 2 * (size_t)n_rows) * sizeof(float);
+    if (smem > 48 * 1024) MX_REFUSE("router: %zu bytes of shared memory for K = %d and %d rows", smem, K, n_rows);
+    if (dtype == MX_DTYPE_F32)
+        moe_route_softmax_kernel<float><<<n_tokens, 256, smem, stream>>>((const float*)h, ld, router, K, n_experts,
+                                                                        n_identity, top, correction, ids, weights,
+                                                                        counts, place);
+    else
+        moe_route_softmax_kernel<__nv_bfloat16><<<n_tokens, 256, smem, stream>>>(
+            (const __nv_bfloat16*)h, ld, router, K, n_experts, n_identity, top, correction, ids, weights, counts, place);
+    return mx_launch_status();
+}
+
 extern "C" int mx_moe_tile_rows() { return MOE_BM; }
 
 extern "C" int mx_moe_plan(const int* counts, const int* ids, const int* place, int n_experts, int n_pairs, int tile_rows,
@@ -372,7 +498,7 @@ extern "C" int mx_moe_plan(const int* counts, const int* ids, const int* place, 
                                                                               tile_map, n_tiles);
     int rc = mx_launch_status();
     if (rc != MX_OK) return rc;
-    moe_scatter_kernel<<<(n_pairs + 255) / 256, 256, 0, stream>>>(ids, place, first, order, n_pairs);
+    moe_scatter_kernel<<<(n_pairs + 255) / 256, 256, 0, stream>>>(ids, place, first, order, n_pairs, n_experts);
     return mx_launch_status();
 }
 
@@ -381,21 +507,26 @@ extern "C" int mx_moe_plan(const int* counts, const int* ids, const int* place, 
 // sorted row, out float [pairs][N] by pair, times pair_weight. `max_tiles` bounds the tiles a step can have.
 extern "C" int mx_moe_gemm(const void* a, int dtype, int lda, const int* order, int a_div, const void* w,
                            long long expert_stride, int N, int K, const int* tile_map, const int* n_tiles, int max_tiles,
-                           void* out, const float* pair_weight, int glu, int act, cudaStream_t stream) {
+                           void* out, const float* pair_weight, int glu, int act, float limit, float slope, float shift,
+                           cudaStream_t stream) {
     if (max_tiles <= 0 || N <= 0) return MX_OK;
     if (max_tiles > 65535) MX_REFUSE("routed feed-forward: %d row tiles exceed the grid", max_tiles);
     const dim3 grid((N + MOE_BN - 1) / MOE_BN, max_tiles);
+    const ClampedAct clamped{limit, slope, shift};
+    if (glu && (act < 0 || act > 2)) MX_REFUSE("routed feed-forward: activation %d", act);
 #define MOE_LAUNCH(T, GLU, ACT)                                                                                        \
     moe_gemm_kernel<T, GLU, ACT><<<grid, 256, 0, stream>>>((const T*)a, lda, order, a_div, (const T*)w, expert_stride, \
-                                                           N, K, tile_map, n_tiles, out, pair_weight)
+                                                           N, K, tile_map, n_tiles, out, pair_weight, clamped)
     if (dtype == MX_DTYPE_F32) {
         if (!glu) MOE_LAUNCH(float, false, 0);
         else if (act == 0) MOE_LAUNCH(float, true, 0);
-        else MOE_LAUNCH(float, true, 1);
+        else if (act == 1) MOE_LAUNCH(float, true, 1);
+        else MOE_LAUNCH(float, true, 2);
     } else {
         if (!glu) MOE_LAUNCH(__nv_bfloat16, false, 0);
         else if (act == 0) MOE_LAUNCH(__nv_bfloat16, true, 0);
-        else MOE_LAUNCH(__nv_bfloat16, true, 1);
+        else if (act == 1) MOE_LAUNCH(__nv_bfloat16, true, 1);
+        else MOE_LAUNCH(__nv_bfloat16, true, 2);
     }
 #undef MOE_LAUNCH
     return mx_launch_status();
@@ -414,24 +545,47 @@ extern "C" int mx_moe_gather(const void* h, int ld, const int* order, int top, v
 
 extern "C" int mx_moe_combine_sorted(const float* rows, const int* ids, const int* place, const int* first,
                                      const float* weight, float* residual, int n_tokens, int top, int width,
+                                     const void* input, int input_dtype, int input_ld, int n_experts,
                                      cudaStream_t stream) {
     const long long count = (long long)n_tokens * width;
     if (count <= 0) return MX_OK;
-    if (width % 4 == 0 && ((uintptr_t)rows | (uintptr_t)residual) % 16 == 0) {
+    if (input == nullptr) n_experts = 0x7fffffff;          // every pair has a row
+    const bool f32 = input == nullptr || input_dtype == MX_DTYPE_F32;
+    if (width % 4 == 0 && ((uintptr_t)rows | (uintptr_t)residual | (uintptr_t)input) % 16 == 0 && input_ld % 4 == 0) {
         const long long count4 = count / 4;
-        moe_combine_sorted_vec_kernel<<<(unsigned)((count4 + 255) / 256), 256, 0, stream>>>(
-            rows, ids, place, first, weight, residual, top, width / 4, count4);
+        const unsigned blocks = (unsigned)((count4 + 255) / 256);
+        if (f32)
+            moe_combine_sorted_vec_kernel<float><<<blocks, 256, 0, stream>>>(
+                rows, ids, place, first, weight, residual, top, width / 4, count4, (const float*)input, input_ld, n_experts);
+        else
+            moe_combine_sorted_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+                rows, ids, place, first, weight, residual, top, width / 4, count4, (const __nv_bfloat16*)input, input_ld,
+                n_experts);
         return mx_launch_status();
     }
-    moe_combine_sorted_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(rows, ids, place, first, weight,
-                                                                                   residual, top, width, count);
+    const unsigned blocks = (unsigned)((count + 255) / 256);
+    if (f32)
+        moe_combine_sorted_kernel<float><<<blocks, 256, 0, stream>>>(
+            rows, ids, place, first, weight, residual, top, width, count, (const float*)input, input_ld, n_experts);
+    else
+        moe_combine_sorted_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+            rows, ids, place, first, weight, residual, top, width, count, (const __nv_bfloat16*)input, input_ld, n_experts);
     return mx_launch_status();
 }
 
-extern "C" int mx_moe_combine(const float* pairs, float* residual, int n_tokens, int top, int width, cudaStream_t stream) {
+extern "C" int mx_moe_combine(const float* pairs, float* residual, int n_tokens, int top, int width, const int* ids,
+                              const float* weight, const void* input, int input_dtype, int input_ld, int n_experts,
+                              cudaStream_t stream) {
     const long long count = (long long)n_tokens * width;
     if (count <= 0) return MX_OK;
-    moe_combine_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(pairs, residual, top, width, count);
+    if (input == nullptr || weight == nullptr) ids = nullptr;
+    const unsigned blocks = (unsigned)((count + 255) / 256);
+    if (input == nullptr || input_dtype == MX_DTYPE_F32)
+        moe_combine_kernel<float><<<blocks, 256, 0, stream>>>(pairs, residual, top, width, count, ids, weight,
+                                                              (const float*)input, input_ld, n_experts);
+    else
+        moe_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(pairs, residual, top, width, count, ids, weight,
+                                                                      (const __nv_bfloat16*)input, input_ld, n_experts);
     return mx_launch_status();
 }
 

@@ -144,7 +144,8 @@ class Scheduler:
             if window is not None:
                 # a window of W keys spans at most ceil((W - 1) / page) + 1 pages, and the next token's
                 # page is taken before the oldest is given back
-                need = min(most_pages, (window - 1 + page_size - 1) // page_size + 2)
+                kept = (self.cache.rules[group].keep_first + page_size - 1) // page_size
+                need = min(most_pages, (window - 1 + page_size - 1) // page_size + 2 + kept)
             if need > pool.num_pages:
                 raise RequestRefused(
                     f"request needs {need} pages in group {group}, the pool has {pool.num_pages}")

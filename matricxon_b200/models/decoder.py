@@ -72,7 +72,13 @@ def model_weight_specs(spec: ModelSpec) -> list[WeightSpec]:
     # tensors that an architecture knows to lie in its model folders without being used: expected, never fetched
     for name, shape in spec.extra.get("unused_tensors", ()):
         specs.append(WeightSpec(name, tuple(shape), role="vector", init="bias"))
-    return specs
+    # a tensor that several parts describe in the same words (a table all layers read) is one tensor
+    unique, seen = [], set()
+    for item in specs:
+        if item not in seen:
+            seen.add(item)
+            unique.append(item)
+    return unique
 
 
 def plan_cache(spec: ModelSpec) -> CachePlan:
@@ -134,6 +140,22 @@ class DecoderModel:
         return model_weight_specs(self.spec)
 
     def load(self, fetch) -> None:
+        # a tensor that several parts name is fetched once and held once
+        names: dict[str, int] = {}
+        for index, layer in enumerate(self.spec.layers):
+            for item in set(part_class("block", layer.block).weight_specs(layer, self.spec.layer_prefix_of(index))):
+                names[item.name] = names.get(item.name, 0) + 1
+        shared = {name for name, count in names.items() if count > 1}
+        if shared:
+            plain_fetch, held = fetch, {}
+
+            def fetch(name):
+                if name not in shared:
+                    return plain_fetch(name)
+                if name not in held:
+                    held[name] = plain_fetch(name)
+                return held[name]
+
         self.embedding = fetch(f"{self.spec.embedding_name}{self.spec.weight_suffix}")
         for layer in self.layers:
             layer.load(fetch)
@@ -182,4 +204,6 @@ class DecoderModel:
         logits = linear(normed, self.head, self.head_bias, EPILOGUE_F32, backend=self.runtime.gemm_backend)
         if self.spec.logit_softcap is not None:
             kernels.softcap(logits, self.spec.logit_softcap)
+        if self.spec.logit_scale != 1.0:
+            kernels.scale_rows(logits, self.spec.logit_scale)
         return logits

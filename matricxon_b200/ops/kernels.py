@@ -377,13 +377,14 @@ def paged_attention(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_t
                     n_kv_heads: int, head_dim: int, window: int | None, scale: float,
                     out: torch.Tensor, status: torch.Tensor, n_splits: int = 1,
                     scratch: torch.Tensor | None = None, softcap: float | None = None,
-                    sink: torch.Tensor | None = None) -> None:
+                    sink: torch.Tensor | None = None, keep_first: int = 0) -> None:
     """Attention of ``n_tokens`` query rows over the paged cache.
 
     ``q`` points at the first query head of row 0 and rows are ``q_stride`` elements apart
     (so the q part of a fused qkv buffer can be used in place). ``out`` is [tokens, heads * dim].
     ``softcap``: scaled scores become ``softcap * tanh(score / softcap)``. ``sink`` (float32, one per
-    head): ``exp(sink[h])`` joins the softmax's denominator and brings no value.
+    head): ``exp(sink[h])`` joins the softmax's denominator and brings no value. ``keep_first``: with a
+    window, the keys at positions below it stay visible at any distance.
     """
     _need(q, "q", contiguous=False)
     _need(cache, "cache", q.dtype)
@@ -404,8 +405,8 @@ def paged_attention(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_t
         _ptr(q), dtype_code(q.dtype), q_stride, _ptr(cache), cache.shape[0], page_size,
         _ptr(block_tables), block_tables.stride(0), _ptr(tok_seq), _ptr(positions), n_tokens,
         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(out), out.stride(0),
-        n_splits, _ptr(scratch), _ptr(status), float(softcap or 0.0), _sink_ptr(sink, n_heads), _stream()),
-        "paged_attention")
+        n_splits, _ptr(scratch), _ptr(status), float(softcap or 0.0), _sink_ptr(sink, n_heads), int(keep_first),
+        _stream()), "paged_attention")
     _launched(2 if n_splits > 1 else 1)
 
 
@@ -481,7 +482,7 @@ def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,
                         n_kv_heads: int, head_dim: int, window: int | None, scale: float,
                         out: torch.Tensor, status: torch.Tensor, n_splits: int = 1,
                         scratch: torch.Tensor | None = None, softcap: float | None = None,
-                        sink: torch.Tensor | None = None) -> None:
+                        sink: torch.Tensor | None = None, keep_first: int = 0) -> None:
     """Tensor-core attention (bfloat16, head_dim 64 or 128). ``tiles`` is int32 [n_tiles, 2]:
     (sequence, first row) of each tile of the (token, head-in-group) rows; ``narrow`` tiles
     hold at most 16 rows, the others 64 (see ``attention_tile_lists``)."""
@@ -510,7 +511,7 @@ def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,
         block_tables.stride(0), _ptr(cu_q), _ptr(context_lens), _ptr(tiles) if tiles is not None else None, n_tiles,
         1 if narrow else 0, n_tokens, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
         _ptr(out), out.stride(0), n_splits, _ptr(scratch), _ptr(status), float(softcap or 0.0),
-        _sink_ptr(sink, n_heads), _stream()), "paged_attention_mma")
+        _sink_ptr(sink, n_heads), int(keep_first), _stream()), "paged_attention_mma")
     _launched(2 if n_splits > 1 else 1)
 
 
@@ -994,6 +995,7 @@ def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
 
 # ---------------------------------------------------------------------- gated and routed feed-forwards
 GLU_ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
+CLAMPED_ACTIVATION = 2       # the grouped product's code for ``min(g, limit) * sigmoid(slope g) * (clamp(u) + shift)``
 
 
 def glu(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
@@ -1057,11 +1059,13 @@ def moe_max_tiles(n_pairs: int, n_experts: int, tile_rows: int | None = None) ->
 
 def moe_gemm(a: torch.Tensor, order: torch.Tensor, a_div: int, w: torch.Tensor, tile_map: torch.Tensor,
              n_tiles: torch.Tensor, max_tiles: int, out: torch.Tensor, pair_weight: torch.Tensor | None,
-             activation: str | None) -> None:
+             activation: str | tuple | None) -> None:
     """The grouped product over the pairs sorted by expert. With ``activation``: ``a`` holds the tokens' rows (pair
     p reads row ``p // a_div``), ``w`` [experts, 2 N, K] stacks gate and up rows, ``out`` [pairs, N] (sorted order,
     dtype of a) = act(gate) * up. Without: ``a`` [pairs, K] is in sorted order, ``w`` [experts, N, K], ``out``
-    float32 [pairs, N] in pair order = ``pair_weight[pair] *`` product."""
+    float32 [pairs, N] in pair order = ``pair_weight[pair] *`` product. ``activation`` is a name of
+    ``GLU_ACTIVATIONS`` or ``("clamped", limit, slope, shift)``: ``g = min(gate, limit)``,
+    ``u = clamp(up, -limit, limit)`` (limit <= 0: neither), ``g * sigmoid(slope g) * (u + shift)``."""
     _need(a, "a")
     _need(w, "w", a.dtype)
     _need(out, "out")
@@ -1076,20 +1080,67 @@ def moe_gemm(a: torch.Tensor, order: torch.Tensor, a_div: int, w: torch.Tensor, 
     else:
         _need(pair_weight, "pair_weight", torch.float32)
         assert out.dtype == torch.float32
+    code, constants = 0, (0.0, 0.0, 0.0)
+    if isinstance(activation, tuple):
+        code, constants = CLAMPED_ACTIVATION, tuple(float(c) for c in activation[1:4])
+    elif glu_form:
+        code = GLU_ACTIVATIONS[activation]
     check(library().mx_moe_gemm(_ptr(a), dtype_code(a.dtype), a.stride(0), _ptr(order), a_div, _ptr(w), w.stride(0), n, k,
                                 _ptr(tile_map), _ptr(n_tiles), max_tiles, _ptr(out), _ptr(pair_weight),
-                                1 if glu_form else 0, GLU_ACTIVATIONS[activation] if glu_form else 0, _stream()),
+                                1 if glu_form else 0, code, *constants, _stream()),
           "moe_gemm")
     _launched()
 
 
-def moe_combine(pairs: torch.Tensor, residual: torch.Tensor, top: int) -> None:
-    """residual[t] += the sum of the token's ``top`` rows of ``pairs`` [tokens * top, width], first slot first."""
+def _identity_arguments(identity, n: int, width: int):
+    """(ids, weights, input, its dtype code, its row stride, experts with rows) of pairs that stand for their
+    token's input (float32 or bfloat16 rows)."""
+    if identity is None:
+        return None, None, None, F32, 0, 0
+    ids, weights, rows, n_experts = identity
+    _need(ids, "ids", torch.int32)
+    _need(weights, "weights", torch.float32)
+    _need(rows, "identity input", contiguous=False)
+    assert tuple(rows.shape) == (n, width) and rows.stride(1) == 1
+    return ids, weights, rows, dtype_code(rows.dtype), rows.stride(0), int(n_experts)
+
+
+def moe_combine(pairs: torch.Tensor, residual: torch.Tensor, top: int, identity=None) -> None:
+    """residual[t] += the sum of the token's ``top`` rows of ``pairs`` [tokens * top, width], first slot first.
+    ``identity`` = (ids, weights, input [tokens, width], n_experts): a pair whose id is ``>= n_experts``
+    has no row; ``weights[pair] * input[t]`` stands for it."""
     _need(pairs, "pairs", torch.float32)
     _need(residual, "residual", torch.float32)
     n, width = residual.shape
     assert tuple(pairs.shape) == (n * top, width)
-    check(library().mx_moe_combine(_ptr(pairs), _ptr(residual), n, top, width, _stream()), "moe_combine")
+    ids, weights, rows, code, ld, n_experts = _identity_arguments(identity, n, width)
+    check(library().mx_moe_combine(_ptr(pairs), _ptr(residual), n, top, width, _ptr(ids), _ptr(weights), _ptr(rows), code,
+                                   ld, n_experts, _stream()), "moe_combine")
+    _launched()
+
+
+def moe_route_softmax(h: torch.Tensor, router: torch.Tensor, top: int, n_identity: int, correction: torch.Tensor | None,
+                      ids: torch.Tensor, weights: torch.Tensor, counts: torch.Tensor, place: torch.Tensor) -> None:
+    """Per token: softmax scores over the rows of the float32 router [experts + n_identity, K]; the ``top`` rows
+    with the largest ``score + correction`` (float32 per row or None; ties to the lower index); weights = the
+    chosen rows' plain scores / their sum. ``counts`` [experts] must be zero; afterwards it holds every expert's
+    pairs and ``place`` each pair's index among them. A pair of one of the last ``n_identity`` rows keeps its id,
+    is counted nowhere and has place 0."""
+    _need(h, "h")
+    _need(router, "router", torch.float32)
+    for name, tensor in (("ids", ids), ("counts", counts), ("place", place)):
+        _need(tensor, name, torch.int32)
+    _need(weights, "weights", torch.float32)
+    n, k = h.shape
+    n_experts = router.shape[0] - n_identity
+    assert router.shape[1] == k and ids.numel() == n * top == weights.numel() == place.numel()
+    assert n_experts >= 0 and counts.numel() == n_experts
+    if correction is not None:
+        _need(correction, "correction", torch.float32)
+        assert correction.numel() == router.shape[0]
+    check(library().mx_moe_route_softmax(_ptr(h), dtype_code(h.dtype), h.stride(0), _ptr(router), k, n_experts, n_identity,
+                                         top, _ptr(correction), _ptr(ids), _ptr(weights), _ptr(counts), _ptr(place), n,
+                                         _stream()), "moe_route_softmax")
     _launched()
 
 
@@ -1139,9 +1190,10 @@ def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_map: torch.Tenso
 
 
 def moe_combine_sorted(rows: torch.Tensor, ids: torch.Tensor, place: torch.Tensor, first: torch.Tensor,
-                       weights: torch.Tensor, residual: torch.Tensor, top: int) -> None:
+                       weights: torch.Tensor, residual: torch.Tensor, top: int, identity=None) -> None:
     """residual[t] += sum over the token's ``top`` pairs of ``weights[pair] * rows[first[ids[pair]] + place[pair]]``
-    (``rows`` float32 [pairs, width] in sorted order), first slot first."""
+    (``rows`` float32 [pairs, width] in sorted order), first slot first. ``identity`` = (input [tokens, width],
+    n_experts): a pair whose id is ``>= n_experts`` has no row; its token's input stands for it."""
     _need(rows, "rows", torch.float32)
     _need(residual, "residual", torch.float32)
     _need(weights, "weights", torch.float32)
@@ -1149,6 +1201,95 @@ def moe_combine_sorted(rows: torch.Tensor, ids: torch.Tensor, place: torch.Tenso
         _need(tensor, name, torch.int32)
     n, width = residual.shape
     assert tuple(rows.shape) == (n * top, width) and ids.numel() == n * top == place.numel() == weights.numel()
+    _, _, source, code, ld, n_experts = _identity_arguments(
+        None if identity is None else (ids, weights, identity[0], identity[1]), n, width)
     check(library().mx_moe_combine_sorted(_ptr(rows), _ptr(ids), _ptr(place), _ptr(first), _ptr(weights), _ptr(residual),
-                                          n, top, width, _stream()), "moe_combine_sorted")
+                                          n, top, width, _ptr(source), code, ld, n_experts, _stream()), "moe_combine_sorted")
+    _launched()
+
+
+# ---------------------------------------------------------------------- branches normalised on their way out
+def layernorm_scaled_add(x: torch.Tensor, branch: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+                         scale: torch.Tensor | None, eps: float, act: torch.Tensor | None = None) -> None:
+    """x[r] += LayerNorm(branch[r]) * weight (+ bias), times ``scale`` entry by entry (a float32 vector or None); float
+    statistics. ``act`` (bfloat16 or float32, same shape) receives the new rows."""
+    _need(x, "x", torch.float32)
+    _need(branch, "branch", torch.float32)
+    _need(weight, "weight", torch.float32)
+    n, hidden = x.shape
+    assert tuple(branch.shape) == (n, hidden) and weight.numel() == hidden
+    for name, tensor in (("bias", bias), ("scale", scale)):
+        if tensor is not None:
+            _need(tensor, name, torch.float32)
+            assert tensor.numel() == hidden
+    if act is not None:
+        _need(act, "act")
+        assert tuple(act.shape) == (n, hidden)
+    check(library().mx_layernorm_scaled_add(_ptr(x), _ptr(branch), _ptr(weight), _ptr(bias), _ptr(scale), _ptr(act),
+                                            dtype_code(act.dtype) if act is not None else F32, n, hidden, float(eps),
+                                            _stream()), "layernorm_scaled_add")
+    _launched()
+
+
+def scale_rows(x: torch.Tensor, factor: float) -> None:
+    """x *= factor (float32, in place)."""
+    _need(x, "x", torch.float32)
+    check(library().mx_scale_rows(_ptr(x), x.numel(), float(factor), _stream()), "scale_rows")
+    _launched()
+
+
+def token_side_input(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, column: int, gate: torch.Tensor,
+                     proj: torch.Tensor, norm: torch.Tensor, eps: float, status: torch.Tensor,
+                     act: torch.Tensor | None = None) -> None:
+    """x[t] += y / sqrt(mean(y^2) + eps) * norm with y = proj (gelu_tanh(gate x[t]) * table[id_t, column:column + dim]),
+    in float, in place. ``table`` [vocab, width], ``gate`` [dim, hidden], ``proj`` [hidden, dim] share a dtype, which
+    ``act`` (the new rows, optional) has too."""
+    _need(x, "x", torch.float32)
+    _need(token_ids, "token_ids", torch.int32)
+    _need(table, "table")
+    _need(gate, "gate", table.dtype)
+    _need(proj, "proj", table.dtype)
+    _need(norm, "norm", torch.float32)
+    _need(status, "status", torch.int32)
+    n, hidden = x.shape
+    dim = gate.shape[0]
+    assert tuple(gate.shape) == (dim, hidden) and tuple(proj.shape) == (hidden, dim) and norm.numel() == hidden
+    assert token_ids.numel() >= n
+    if act is not None:
+        _need(act, "act", table.dtype)
+        assert tuple(act.shape) == (n, hidden)
+    check(library().mx_token_side_input(_ptr(x), _ptr(act), _ptr(token_ids), _ptr(table), table.shape[1], int(column),
+                                        table.shape[0], _ptr(gate), _ptr(proj), _ptr(norm), dtype_code(table.dtype), n,
+                                        hidden, dim, float(eps), _ptr(status), _stream()), "token_side_input")
+    _launched()
+
+
+def rotate_norm_kv_write(proj: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, rot: int, eps: float | None,
+                         slots: torch.Tensor | None, cache: torch.Tensor | None, q_out: torch.Tensor, n_heads: int,
+                         n_kv_heads: int, dim: int, vdim: int, status: torch.Tensor) -> None:
+    """From float rows ``[q | k | v | ...]`` of a fused projection: q and k heads rotated over their first ``rot``
+    entries (pairs (i, i + rot/2), angle ``position * freq[i]``) and then divided by their root mean square over
+    ``dim`` (``eps`` inside the root; None: not divided); q into ``q_out`` [tokens, heads * hd], k and v into the
+    paged ``cache`` [pages, 2, kv heads, page_size, hd] at ``slots`` (both None: nothing is stored). ``hd`` is the
+    padded head size of ``q_out``; tails are zero."""
+    _need(proj, "proj", torch.float32, contiguous=False)
+    _need(positions, "positions", torch.int32)
+    _need(freq, "freq", torch.float32)
+    _need(q_out, "q_out")
+    _need(status, "status", torch.int32)
+    n = q_out.shape[0]
+    hd = q_out.shape[1] // n_heads
+    assert q_out.shape[1] == n_heads * hd and proj.stride(1) == 1 and proj.shape[0] >= n
+    assert freq.numel() >= rot // 2
+    n_pages, page_size = 0, 1
+    if cache is not None:
+        _need(cache, "cache", q_out.dtype)
+        _need(slots, "slots", torch.int32)
+        n_pages, page_size = cache.shape[0], cache.shape[3]
+        assert tuple(cache.shape[1:]) == (2, n_kv_heads, page_size, hd), cache.shape
+    check(library().mx_rotate_norm_kv_write(_ptr(proj), proj.stride(0), _ptr(positions), _ptr(freq), int(rot),
+                                            -1.0 if eps is None else float(eps), _ptr(slots) if cache is not None else None,
+                                            _ptr(cache), n_pages, page_size, _ptr(q_out), dtype_code(q_out.dtype), n,
+                                            n_heads, n_kv_heads, dim, vdim, hd, _ptr(status), _stream()),
+          "rotate_norm_kv_write")
     _launched()

@@ -100,27 +100,33 @@ def simt_splits(ctx, n_heads: int, n_kv_heads: int, head_dim: int, window: int |
 
 
 def paged_attend(q, q_stride, ctx, binding, rt, n_heads, n_kv_heads, head_dim, window, scale, softcap=None,
-                 sink=None):
+                 sink=None, keep_first=0):
     """Attention of the step's query rows (``q``: query head h of a row at column ``h * head_dim``, rows
     ``q_stride`` apart) over the keys and values already stored in ``binding.kv``: picks the kernel, the
     tiles and the key splits for this step. Returns [tokens, heads * head_dim] in the runtime dtype.
     ``softcap`` caps the scaled scores at ``softcap * tanh(score / softcap)``; ``sink`` (float32, one logit per
-    head) joins the softmax's denominator without a value. Every kernel takes both."""
+    head) joins the softmax's denominator without a value. ``keep_first``: under a window, the keys of the
+    sequence's first ``keep_first`` positions stay visible at any distance. Every kernel takes cap and sink; the
+    tcgen05 kernel walks one unbroken run of keys, so windows with kept first tokens go to the mma.sync tiles."""
+    keep_first = int(keep_first) if window is not None else 0
     extras = {"softcap": softcap, "sink": sink}
+    kept = {"keep_first": keep_first}
+    # the kept keys are walked beside the window's: the span that sizes the key splits grows by them
+    span = None if window is None else window + keep_first
     group = ctx.groups[binding.group]
     attn = torch.empty((ctx.n_tokens, n_heads * head_dim), dtype=rt.dtype, device=q.device)
     if kernels.mma_attention_supported(rt.dtype, head_dim, rt.page_size, q_stride):
         group_size = n_heads // n_kv_heads
         # prompt portions on tcgen05 when the kernel takes the geometry, else on mma.sync
-        on_tc = _TC_ATTENTION and kernels.tc_attention_supported(rt.dtype, head_dim, rt.page_size,
-                                                                 q_stride, group_size)
+        on_tc = _TC_ATTENTION and keep_first == 0 and kernels.tc_attention_supported(
+            rt.dtype, head_dim, rt.page_size, q_stride, group_size)
         narrow, n_narrow, wide, n_wide = attention_tiles(ctx, group_size, token_tiles=on_tc)
         for tiles, n_tiles, is_narrow in ((narrow, n_narrow, True), (wide, n_wide, False)):
             if n_tiles == 0:
                 continue
             if on_tc and not is_narrow:
                 n_splits, scratch = tc_tile_splits(ctx, n_tiles, n_narrow == 0, n_heads,
-                                                       n_kv_heads, head_dim, window)
+                                                       n_kv_heads, head_dim, span)
                 kernels.paged_attention_tc(q, q_stride, binding.kv, group.block_tables, ctx.cu_q,
                                            ctx.context_lens, tiles, n_tiles, ctx.n_tokens,
                                            n_heads, n_kv_heads, head_dim,
@@ -131,19 +137,19 @@ def paged_attend(q, q_stride, ctx, binding, rt, n_heads, n_kv_heads, head_dim, w
             if is_narrow and ctx.padded:
                 tiles, n_tiles = None, ctx.n_seqs      # a batch of decoding requests: tile i is sequence i
             n_splits, scratch = mma_tile_splits(ctx, n_tiles, is_narrow, alone, n_heads,
-                                                n_kv_heads, head_dim, window)
+                                                n_kv_heads, head_dim, span)
             kernels.paged_attention_mma(q, q_stride, binding.kv, group.block_tables,
                                         ctx.cu_q, ctx.context_lens, tiles, n_tiles, is_narrow,
                                         ctx.n_tokens, n_heads, n_kv_heads,
                                         head_dim, window, scale, attn, ctx.status,
-                                        n_splits=n_splits, scratch=scratch, **extras)
+                                        n_splits=n_splits, scratch=scratch, **extras, **kept)
     else:
         n_splits, scratch = simt_splits(ctx, n_heads, n_kv_heads,
-                                                 head_dim, window)
+                                                 head_dim, span)
         kernels.paged_attention(q, q_stride, binding.kv, group.block_tables, ctx.tok_seq,
                                 ctx.positions, ctx.n_tokens, n_heads, n_kv_heads,
                                 head_dim, window, scale, attn, ctx.status,
-                                n_splits=n_splits, scratch=scratch, **extras)
+                                n_splits=n_splits, scratch=scratch, **extras, **kept)
     return attn
 
 
@@ -406,6 +412,79 @@ class SinkAttention(Mixer):
             kernels.head_gate(attn, proj[:, gate_col:gate_col + s.num_heads], gated, s.num_heads, s.value_dim)
             attn = gated
         elif hd != s.value_dim:
+            attn = attn.view(n, s.num_heads, hd)[:, :, :s.value_dim].reshape(n, -1)
+        if residual is None:
+            return linear(attn, self.o_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
+        return linear(attn, self.o_weight, None, EPILOGUE_RESIDUAL, residual=residual, out=residual,
+                      backend=rt.gemm_backend, defer_sum=getattr(ctx, "sums_may_pend", False))
+
+
+@register_part("mixer", "unit_norm_attention")
+class UnitNormAttention(Mixer):
+    """Grouped-query attention without biases whose queries and keys are rotated over the first entries of every
+    head and then divided by their root mean square, head by head, with no learned weight; a window that keeps
+    the sequence's first tokens in sight; values of a width of their own (``UnitNormAttentionSpec``).
+
+    One fused product gives float rows ``[q | k | v]``; one kernel rotates and normalises q and k in float and
+    stores k and v in the paged cache in the layout the stock attention kernels read (``paged_attend``, which
+    knows the window's kept first tokens), every head padded with zeros to a common size of a multiple of 16
+    when the key and value widths differ or are no such multiple. ``forward(h, None, ...)`` returns the mixer's
+    float output without a residual."""
+
+    capturable = True
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        self.padded_dim = self.cache_head_dim(spec)
+        self.position = (build_part("position", spec.position, runtime, prefix)
+                         if spec.position is not None and spec.position.rotary_dim > 0 else None)
+
+    @staticmethod
+    def cache_head_dim(spec) -> int:
+        return -(-max(spec.head_dim, spec.value_dim) // 16) * 16
+
+    @classmethod
+    def _matrices(cls, spec):
+        return [(spec.query_name, (spec.num_heads * spec.head_dim, spec.hidden_size)),
+                (spec.key_name, (spec.num_kv_heads * spec.head_dim, spec.hidden_size)),
+                (spec.value_name, (spec.num_kv_heads * spec.value_dim, spec.hidden_size))]
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        specs = [WeightSpec(prefix + name, shape, role="matrix", init="weight") for name, shape in cls._matrices(spec)]
+        specs.append(WeightSpec(prefix + spec.output_name, (spec.hidden_size, spec.num_heads * spec.value_dim),
+                                role="matrix", init="weight"))
+        return specs
+
+    @classmethod
+    def cache_request(cls, spec):
+        return KVCacheRequest(num_kv_heads=spec.num_kv_heads, head_dim=cls.cache_head_dim(spec), window=spec.window,
+                              keep_first=spec.keep_first if spec.window is not None else 0)
+
+    def load(self, fetch):
+        p, s = self.prefix, self.spec
+        self.proj_weight = torch.cat([fetch(p + name) for name, _ in self._matrices(s)])
+        self.o_weight = fetch(p + s.output_name)
+
+    def forward(self, h, residual, ctx, binding):
+        s, rt, hd = self.spec, self.runtime, self.padded_dim
+        if binding.kv is None:
+            raise RuntimeError("attention needs cache pages bound to it")
+        n = h.shape[0]
+        proj = linear(h, self.proj_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
+        q = torch.empty((n, s.num_heads * hd), dtype=rt.dtype, device=h.device)
+        writes = binding.writes
+        if self.position is not None:
+            freq, rot = self.position.frequencies, s.position.rotary_dim
+        else:
+            freq, rot = torch.empty(0, dtype=torch.float32, device=h.device), 0
+        kernels.rotate_norm_kv_write(proj, ctx.positions, freq, rot, s.eps if s.unit_norm else None,
+                                     ctx.groups[binding.group].slots if writes else None,
+                                     binding.kv if writes else None, q, s.num_heads, s.num_kv_heads, s.head_dim,
+                                     s.value_dim, ctx.status)
+        attn = paged_attend(q, q.stride(0), ctx, binding, rt, s.num_heads, s.num_kv_heads, hd, s.window, s.scale,
+                            keep_first=s.keep_first)
+        if hd != s.value_dim:
             attn = attn.view(n, s.num_heads, hd)[:, :, :s.value_dim].reshape(n, -1)
         if residual is None:
             return linear(attn, self.o_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)

@@ -16,6 +16,7 @@ Interfaces (duck-typed; these base classes state them):
   Mixer.forward(h, residual, ctx, binding) -> residual + mix(h)      (float32)
   Mixer.cache_request(spec) / Mixer.state_request(spec): what the cache manager must hold.
   FeedForward.forward(h, residual, ctx) -> residual + ffn(h)          (float32)
+  SideInput.forward(x, ctx) -> (x, activations)                        (x updated in place)
   Block.forward(x, ctx, binding) -> x                                  (float32)
 """
 
@@ -28,7 +29,7 @@ import torch
 
 from matricxon_b200.weights.loader import WeightSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "side_input", "block")
 _PARTS: dict[str, dict[str, type]] = {category: {} for category in CATEGORIES}
 
 
@@ -84,12 +85,14 @@ class KVCacheRequest:
     ``num_kv_heads = 1`` and its vector's width as ``head_dim``. How a tile is laid out inside is
     the mixer's own business: the cache manager deals in pages, never in their contents.
     ``window`` None keeps every position; otherwise pages wholly older than the last
-    ``window`` positions are given back."""
+    ``window`` positions are given back, except those that hold any of the sequence's first
+    ``keep_first`` positions."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None
     planes: int = 2
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -173,6 +176,14 @@ class Mixer(Part):
 
 class FeedForward(Part):
     def forward(self, h, residual, ctx):
+        raise NotImplementedError
+
+
+class SideInput(Part):
+    """Something a layer adds to the residual stream after its sublayers. ``forward(x, ctx)`` updates the float
+    stream in place and returns (x, activations): the new rows in the runtime dtype (x itself in float32)."""
+
+    def forward(self, x, ctx):
         raise NotImplementedError
 
 

@@ -3,6 +3,11 @@
 ``pre_norm_sequential``: ``x = x + mixer(norm1(x)); x = x + ffn(norm2(x))``
 (app/architectures/starcoder2_layers.py:67-68); a layer without a feed-forward has only the first sublayer. The residual stream ``x`` is float32
 and each sub-layer adds into it in float.
+
+``post_norm_sequential``: ``x = norm1(a x + mixer(x)); x = norm2(a x + ffn(x))``.
+
+``branch_norm_sequential``: ``x = x + s1 * norm1(mixer(x)); x = x + s2 * norm2(ffn(x))`` with learned vectors
+``s1``, ``s2`` (optional), then whatever the layer adds from outside the stream (``LayerSpec.side_input``).
 """
 
 from __future__ import annotations
@@ -144,3 +149,89 @@ class PostNormSequentialBlock(Block):
             x, h = self.ffn_norm.forward_scaled_sum(x, fed, self.spec.skip_scale)
         ctx.memo["stream_activations"] = (x, h)
         return x
+
+
+@register_part("block", "branch_norm_sequential")
+class BranchNormSequentialBlock(Block):
+    """Norm on the branch only: ``x = x + s1 * norm1(mixer(x)); x = x + s2 * norm2(ffn(x))``. The sublayers read
+    ``x`` itself (in the runtime dtype, which the kernel that ends a sublayer writes beside the float stream); only
+    a sublayer's own output is normalised, then scaled entry by entry by a learned vector
+    (``LayerSpec.branch_scale_names``; None: no scale) and added in float. A layer without a feed-forward has only
+    the first sublayer. After the sublayers the layer's ``side_input`` part, if it has one, adds its own term."""
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        if not hasattr(part_class_of("norm", spec.mixer_norm), "forward_scaled_add"):
+            raise ValueError(f"norm {spec.mixer_norm.kind!r} cannot end a branch (no forward_scaled_add)")
+        self.mixer = build_part("mixer", spec.mixer, runtime, f"{prefix}{spec.mixer_name}")
+        self.mixer_norm = build_part("norm", spec.mixer_norm, runtime, f"{prefix}{spec.mixer_norm_name}")
+        self.feed_forward = self.ffn_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, runtime,
+                                           f"{prefix}{spec.feed_forward_name}")
+            self.ffn_norm = build_part("norm", spec.ffn_norm, runtime, f"{prefix}{spec.ffn_norm_name}")
+        self.side_input = (build_part("side_input", spec.side_input, runtime, f"{prefix}{spec.side_input_name}")
+                           if spec.side_input is not None else None)
+        self.mixer_scale = self.ffn_scale = None
+        self.capturable = all(part.capturable for part in self.parts())
+
+    @classmethod
+    def _scale_names(cls, spec, prefix):
+        mixer_scale, ffn_scale = spec.branch_scale_names
+        if spec.feed_forward is None:
+            ffn_scale = None
+        return (prefix + mixer_scale if mixer_scale is not None else None,
+                prefix + ffn_scale if ffn_scale is not None else None)
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        from matricxon_b200.parts.base import part_class
+        from matricxon_b200.weights.loader import WeightSpec
+
+        groups = [("mixer", spec.mixer, spec.mixer_name), ("norm", spec.mixer_norm, spec.mixer_norm_name)]
+        if spec.feed_forward is not None:
+            groups += [("feed_forward", spec.feed_forward, spec.feed_forward_name),
+                       ("norm", spec.ffn_norm, spec.ffn_norm_name)]
+        if spec.side_input is not None:
+            groups.append(("side_input", spec.side_input, spec.side_input_name))
+        out = []
+        for category, sub, name in groups:
+            out.extend(part_class(category, sub.kind).weight_specs(sub, f"{prefix}{name}"))
+        width = spec.mixer_norm.size
+        for name in cls._scale_names(spec, prefix):
+            if name is not None:
+                out.append(WeightSpec(name, (width,), role="vector", init="norm_weight"))
+        return out
+
+    def parts(self):
+        return tuple(part for part in (self.mixer, self.mixer_norm, self.feed_forward, self.ffn_norm, self.side_input)
+                     if part is not None)
+
+    def load(self, fetch):
+        for part in self.parts():
+            part.load(fetch)
+        mixer_scale, ffn_scale = self._scale_names(self.spec, self.prefix)
+        self.mixer_scale = fetch(mixer_scale) if mixer_scale is not None else None
+        self.ffn_scale = fetch(ffn_scale) if ffn_scale is not None else None
+
+    _activations = PostNormSequentialBlock._activations
+
+    def forward(self, x, ctx, binding):
+        if isinstance(x, PendingSum):
+            x = x.tensor()
+        h = self._activations(x, ctx)
+        mixed = self.mixer.forward(h, None, ctx, binding)
+        x, h = self.mixer_norm.forward_scaled_add(x, mixed, self.mixer_scale)
+        if self.feed_forward is not None:
+            fed = self.feed_forward.forward(h, None, ctx)
+            x, h = self.ffn_norm.forward_scaled_add(x, fed, self.ffn_scale)
+        if self.side_input is not None:
+            x, h = self.side_input.forward(x, ctx)
+        ctx.memo["stream_activations"] = (x, h)
+        return x
+
+
+def part_class_of(category, spec):
+    from matricxon_b200.parts.base import part_class
+
+    return part_class(category, spec.kind)

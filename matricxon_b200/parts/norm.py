@@ -22,14 +22,14 @@ class LayerNorm(Norm):
 
     @classmethod
     def weight_specs(cls, spec, prefix):
-        specs = [WeightSpec(prefix + "weight", (spec.size,), role="vector", init="norm_weight")]
+        specs = [WeightSpec(prefix + spec.weight_name, (spec.size,), role="vector", init="norm_weight")]
         if spec.bias:
-            specs.append(WeightSpec(prefix + "bias", (spec.size,), role="vector", init="norm_bias"))
+            specs.append(WeightSpec(prefix + spec.bias_name, (spec.size,), role="vector", init="norm_bias"))
         return specs
 
     def load(self, fetch):
-        self.weight = fetch(self.prefix + "weight")
-        self.bias = fetch(self.prefix + "bias") if self.spec.bias else None
+        self.weight = fetch(self.prefix + self.spec.weight_name)
+        self.bias = fetch(self.prefix + self.spec.bias_name) if self.spec.bias else None
 
     def forward(self, x, out=None, rows=None):
         n_rows = x.shape[0] if rows is None else rows.numel()
@@ -45,6 +45,18 @@ class LayerNorm(Norm):
         out = torch.empty(tuple(x.shape), dtype=self.runtime.dtype, device=x.device)
         kernels.layernorm_sum(x, pending.acc, pending.bias, self.weight, self.bias, self.spec.eps, out)
         return x, out
+
+
+    def forward_scaled_add(self, x, branch, scale=None):
+        """``x <- x + norm(branch) * scale`` in place (both float32; ``scale`` a float32 vector or None): the
+        end of a sublayer whose own output is normalised. Returns (x, activations): the new rows in the runtime
+        dtype, which is ``x`` itself on the 32-bit path."""
+        if self.runtime.dtype == torch.float32:
+            kernels.layernorm_scaled_add(x, branch, self.weight, self.bias, scale, self.spec.eps)
+            return x, x
+        act = torch.empty(tuple(x.shape), dtype=self.runtime.dtype, device=x.device)
+        kernels.layernorm_scaled_add(x, branch, self.weight, self.bias, scale, self.spec.eps, act)
+        return x, act
 
 
 @register_part("norm", "rmsnorm")

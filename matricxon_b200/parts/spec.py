@@ -23,11 +23,15 @@ from typing import Any
 
 @dataclass(frozen=True)
 class LayerNormSpec:
-    """``(x - mean) / sqrt(var + eps) * weight (+ bias)`` over the last axis."""
+    """``(x - mean) / sqrt(var + eps) * weight (+ bias)`` over the last axis. The tensors are called
+    ``<prefix><weight_name>`` and ``<prefix><bias_name>``; an empty ``weight_name`` makes the prefix itself the
+    weight's name."""
 
     size: int
     eps: float
     bias: bool = True
+    weight_name: str = "weight"
+    bias_name: str = "bias"
     kind: str = "layernorm"
 
 
@@ -189,6 +193,72 @@ class GatedAttentionSpec:
         if self.head_dim <= 0 or self.value_dim <= 0 or max(self.head_dim, self.value_dim) > 256:
             raise ValueError(f"head sizes {self.head_dim} / {self.value_dim} are outside 1..256: "
                              "no attention kernel of this engine takes them")
+
+
+@dataclass(frozen=True)
+class UnitNormAttentionSpec:
+    """Causal grouped-query attention without biases whose queries and keys are rotated over the first entries of
+    every head (``position``; None: no rotation) and then divided, head by head, by their root mean square over
+    ``head_dim`` (eps inside the root, no learned weight; ``unit_norm`` False leaves them as they are). Scores are
+    ``q . k * scale`` under an ordinary softmax; values are ``value_dim`` wide.
+
+    ``window`` None: every earlier key is seen. Otherwise the query at p sees key j iff ``j <= p`` and
+    (``p - j < window`` or ``j < keep_first``): the sequence's first ``keep_first`` tokens stay in sight for good,
+    at their true positions."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    window: int | None
+    keep_first: int
+    scale: float
+    eps: float
+    position: Any | None
+    query_name: str
+    key_name: str
+    value_name: str
+    output_name: str
+    unit_norm: bool = True
+    kind: str = "unit_norm_attention"
+
+    def __post_init__(self) -> None:
+        if self.num_kv_heads <= 0 or self.num_heads % self.num_kv_heads != 0:
+            raise ValueError(f"{self.num_heads} attention heads are no multiple of {self.num_kv_heads} kv heads")
+        if self.head_dim <= 0 or self.value_dim <= 0 or max(self.head_dim, self.value_dim) > 256:
+            raise ValueError(f"head sizes {self.head_dim} / {self.value_dim} are outside 1..256: "
+                             "no attention kernel of this engine takes them")
+        if self.window is not None and self.window <= 0:
+            raise ValueError(f"a window holds at least the query's own position, got {self.window}")
+        if self.keep_first < 0:
+            raise ValueError(f"the number of first tokens kept in sight cannot be negative, got {self.keep_first}")
+        if self.position is not None and self.position.rotary_dim > self.head_dim:
+            raise ValueError(f"{self.position.rotary_dim} rotated entries exceed the head of {self.head_dim}")
+
+
+@dataclass(frozen=True)
+class TokenSideInputSpec:
+    """What a layer adds to the stream from the token itself. A table shared by all layers (``table_name``, a full
+    tensor name, [vocab, table_width]) holds for every token a vector per layer; this layer reads the columns
+    ``[column, column + dim)``: ``g = gelu_tanh(G x) * e``, ``y = P g``, ``x <- x + y / rms(y) * norm`` with
+    ``rms(y) = sqrt(mean(y^2) + eps)``. G, P and the norm's weight lie under the part's prefix."""
+
+    hidden_size: int
+    vocab_size: int
+    dim: int
+    column: int
+    table_width: int
+    eps: float
+    table_name: str
+    gate_name: str
+    proj_name: str
+    norm_name: str
+    kind: str = "token_side_input"
+
+    def __post_init__(self) -> None:
+        if self.dim <= 0 or self.column < 0 or self.column + self.dim > self.table_width:
+            raise ValueError(f"columns {self.column}..{self.column + self.dim} lie outside a table of {self.table_width}")
 
 
 @dataclass(frozen=True)
@@ -378,7 +448,14 @@ class RoutedExpertsSpec:
     ``<prefix><expert_format.format(index=e)>``), of which a token runs ``top``. Router logits ``R h`` and scores
     ``sigmoid`` are float. The experts form ``num_groups`` equal runs of neighbours; a run is worth the sum of its
     ``group_best`` largest scores and only the ``groups_kept`` best runs may supply experts. The output is the sum
-    of the chosen experts' outputs weighted by ``score / (sum of chosen scores + norm_eps) * route_scale``."""
+    of the chosen experts' outputs weighted by ``score / (sum of chosen scores + norm_eps) * route_scale``.
+
+    ``score="softmax"`` is another rule: scores are the softmax over all router rows, the ``top`` rows with the
+    largest ``score + correction`` win (``correction_name``: a float per row, None: none) and the weights use the
+    plain scores; there are no groups and no ``route_scale``. The router then has ``num_experts + num_identity``
+    rows, the last ``num_identity`` of which stand for experts without tensors whose output is their input.
+    ``expert`` may be a ``GatedMlpSpec`` or a ``ClampedGluSpec``. ``shared`` (a feed-forward spec, tensors under
+    ``<prefix><shared_name>``) runs for every token and is added."""
 
     hidden_size: int
     num_experts: int
@@ -391,11 +468,28 @@ class RoutedExpertsSpec:
     expert_format: str = "e{index}."
     group_best: int = 2
     norm_eps: float = 1e-20
+    score: str = "sigmoid"
+    correction_name: str | None = None
+    num_identity: int = 0
+    shared: Any | None = None
+    shared_name: str = "shared."
     kind: str = "routed_experts"
 
     def __post_init__(self) -> None:
-        if not 0 < self.top <= self.num_experts:
-            raise ValueError(f"a token cannot run {self.top} of {self.num_experts} experts")
+        if self.score not in ("sigmoid", "softmax"):
+            raise ValueError(f"router scores are 'sigmoid' or 'softmax', not {self.score!r}")
+        if self.num_identity < 0 or self.num_experts < 0:
+            raise ValueError("expert counts cannot be negative")
+        if self.score == "sigmoid" and (self.num_identity or self.correction_name is not None):
+            raise ValueError("experts without tensors and a correction of the choice belong to the softmax rule")
+        if self.score == "softmax" and (self.num_groups != 1 or self.route_scale != 1.0):
+            raise ValueError("the softmax rule has neither groups nor a scale of its weights")
+        if not 0 < self.top <= self.num_experts + self.num_identity:
+            raise ValueError(f"a token cannot run {self.top} of {self.num_experts + self.num_identity} experts")
+        if self.score == "softmax":
+            if self.norm_eps != 1e-20:
+                raise ValueError("the routing kernel adds 1e-20 to the sum")
+            return
         if self.num_groups <= 0 or self.num_experts % self.num_groups:
             raise ValueError(f"{self.num_experts} experts cannot form {self.num_groups} equal groups")
         if not 0 < self.groups_kept <= self.num_groups:
@@ -423,6 +517,12 @@ class LayerSpec:
     ffn_norm_name: str
     block: str = "pre_norm_sequential"
     skip_scale: float = 1.0
+    # blocks that scale a branch entry by entry before it joins the stream: the tensors' name fragments under the
+    # layer's prefix for the mixer's and the feed-forward's branch (None: no scale)
+    branch_scale_names: tuple[str | None, str | None] = (None, None)
+    # what the layer adds to the stream after its sublayers (``TokenSideInputSpec``; None: nothing) and its fragment
+    side_input: Any | None = None
+    side_input_name: str = ""
     # what the pre-norm block puts behind a part's name fragment to make its prefix ("" for checkpoints whose
     # fragments carry their own separators, as the post-norm block expects them)
     part_separator: str = "."
@@ -463,6 +563,7 @@ class ModelSpec:
     embedding_scale: float = 1.0
     head_bias: bool = False
     logit_softcap: float | None = None
+    logit_scale: float = 1.0             # logits times a constant
     # how names are put together: "<embedding_name><weight_suffix>", a layer's prefix from
     # ``layer_prefix_format`` (fields {prefix} and {index}), the final norm's prefix (None:
     # "<final_norm_name>.")
