@@ -17,6 +17,8 @@ beside StarCoder2 at equal width, heads, layers and feed-forward parameters (pre
 step and in 512-token steps, decode steps at several batch sizes; random weights of both).
 ``--compare parunex`` does the same for the Parunex architecture beside Busatar, the closest of the engine's other
 models (mixed attention and recurrent layers, gated feed-forwards, a float residual stream).
+``--compare bafusun`` does the same for the Bafusun architecture beside Parunex, the closest of the engine's other
+models (rotated windowed attention, routed experts through the same grouped products, a float residual stream).
 """
 
 from __future__ import annotations
@@ -377,6 +379,26 @@ def parunex_config(size: dict) -> dict:
             "norm": {"eps": 1e-5}, "layers": layers}
 
 
+BAFUSUN_KEEP_FIRST = 64
+BAFUSUN_SIDE_DIM = 128
+
+
+def bafusun_config(size: dict) -> dict:
+    """Attention in every layer (128-wide heads over 4 KV heads, a window of 4,096 tokens that keeps the first 64
+    in sight), every layer with eight experts of 3/8 of the dense width and two experts that return their input,
+    two per token, and a shared expert of a quarter of the dense width: the active feed-forward parameters of a
+    token that draws two experts with matrices equal the dense feed-forward's. Every layer takes 128 numbers from
+    the token itself."""
+    w, h = size["width"], size["width"] // 128
+    mixer = {"heads": h, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5 * 4.0,
+             "rot": {"base": 1000000.0, "dims": 64}, "mask": {"size": COMPARE_WINDOW, "keep_first": BAFUSUN_KEEP_FIRST}}
+    mlp = {"kind": "moe", "expert": {"ff": size["ff"] * 3 // 8, "limit": 7.0},
+           "router": {"experts": 8, "identity": 2, "top": 2}, "shared": {"ff": size["ff"] // 4, "limit": 7.0}}
+    layers = [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(COMPARE_LAYERS)]
+    return {"architecture": "Bafusun", "vocab": COMPARE_VOCAB, "width": w, "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "norm": {"eps": 1e-5}, "token_side": {"dim": BAFUSUN_SIDE_DIM}, "layers": layers}
+
+
 def starcoder2_like(size: dict) -> dict:
     return dict(STARCODER2_3B, num_hidden_layers=COMPARE_LAYERS, hidden_size=size["width"],
                 num_attention_heads=size["width"] // 128, num_key_value_heads=4, head_dim=128,
@@ -474,7 +496,9 @@ def compare_designs(args) -> int:
     clocks.start()
     sizes = [s for s in args.compare_sizes.split(",") if s]
     batches = [int(b) for b in args.compare_batches.split(",")]
-    if args.compare == "parunex":
+    if args.compare == "bafusun":
+        designs = (("bafusun", bafusun_config), ("parunex", parunex_config))
+    elif args.compare == "parunex":
         designs = (("parunex", parunex_config), ("busatar", busatar_config))
     else:
         designs = (("busatar", busatar_config), ("starcoder2", starcoder2_like))
@@ -515,9 +539,9 @@ def main() -> int:
                         help="leave out the 7B and 15B workloads through the scheduler")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch every kernel of a decode step by itself (for profilers)")
-    parser.add_argument("--compare", choices=["busatar", "parunex"], default=None,
-                        help="instead of the headline workload: Busatar beside StarCoder2, or Parunex beside Busatar, "
-                             "at equal layer sizes (prefill and decode throughput at a few sizes)")
+    parser.add_argument("--compare", choices=["busatar", "parunex", "bafusun"], default=None,
+                        help="instead of the headline workload: Busatar beside StarCoder2, Parunex beside Busatar, or "
+                             "Bafusun beside Parunex, at equal layer sizes (prefill and decode throughput at a few sizes)")
     parser.add_argument("--compare-only", default=None,
                         help="with --compare: measure only this one of the two designs (for profilers)")
     parser.add_argument("--compare-sizes", default="w1024,w2048")

@@ -81,7 +81,7 @@ class BafusunFeedForward:
         if kind != "moe":
             raise ConfigError(f"{where}: unknown feed-forward kind {kind!r}; Bafusun has 'moe'")
         router = ConfigReader(_object(raw, "router", where), where + ".router")
-        experts, identity = router.integer("experts", minimum=0), router.integer("identity", 0, minimum=0)
+        experts, identity = router.integer("experts", minimum=1), router.integer("identity", 0, minimum=0)
         top = router.integer("top", minimum=1)
         if top > experts + identity:
             raise ConfigError(f"{where}.router: 'top' ({top}) exceeds the {experts + identity} router outputs")

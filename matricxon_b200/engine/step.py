@@ -143,6 +143,12 @@ class StepRunner:
         limit = max_model_len or model.spec.max_position_embeddings
         self.graph_table_width = (limit + cache.page_size - 1) // cache.page_size
         self.use_graphs = use_graphs and getattr(model, "capturable", False)
+        # names of what a caller wants to see of every step beside its logits: each becomes a list in the step's
+        # ``memo`` that the model or a part fills ("layer_outputs": the stream after every schedule entry;
+        # "expert_choices": per routed feed-forward, the experts of every token [tokens, top]); ``last_taps``
+        # holds the lists of the last step
+        self.taps: tuple[str, ...] = ()
+        self.last_taps: dict[str, list] = {}
         self.max_graph_batch = max_graph_batch
         self._graphs: dict[int, tuple] = {}
         # steps that are not pure decoding are captured too, one graph per exact shape (how many
@@ -510,8 +516,11 @@ class StepRunner:
 
     def _run_eager(self, entries: list[StepEntry]) -> torch.Tensor | None:
         ctx = self.build(entries)
+        for name in self.taps:
+            ctx.memo[name] = []
         launches_before = kernels.launch_count
         logits = self._forward(ctx)
+        self.last_taps = {name: ctx.memo[name] for name in self.taps}
         self.launches_per_step = kernels.launch_count - launches_before
         return logits
 
@@ -609,14 +618,15 @@ class StepRunner:
         exact shape from the second time that shape is seen. The logits a replay returns live in
         the graph's memory and are overwritten by the next step of that shape."""
         started = time.perf_counter()
-        bucket = self._graph_bucket(entries)
+        # a step that is listened to runs launch by launch: what a part hands out is not kept by a graph
+        bucket = self._graph_bucket(entries) if not self.taps else None
         try:
             if token_feed is not None and bucket is None:
                 raise StepError("only a captured decode step can take its token ids from the device")
             if bucket is not None:
                 logits = self._run_graph(entries, bucket, token_feed)
             else:
-                key = self._shape_key(entries)
+                key = self._shape_key(entries) if not self.taps else None
                 logits = self._run_shape_graph(entries, key) if key is not None else self._run_eager(entries)
         except OutOfPages:
             raise

@@ -100,6 +100,9 @@ class RoutedExperts(FeedForward):
         else:
             kernels.moe_route(h, self.router, s.top, s.num_groups, s.groups_kept, s.route_scale, ids, weights, counts,
                               place)
+        choices = ctx.memo.get("expert_choices") if hasattr(ctx, "memo") else None
+        if choices is not None:            # a caller listens (``StepRunner.taps``)
+            choices.append(ids.view(n, s.top).clone())
         kernels.moe_plan(counts, ids, place, first, tile_map, n_tiles, order, tile_rows)
         if self.shared is not None:
             # the shared feed-forward's float output is the sum's first term (added to the stream if there is one)

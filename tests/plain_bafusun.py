@@ -116,11 +116,35 @@ def route(h, w, p, router):
     return chosen, picked / (picked.sum(dim=-1, keepdim=True) + 1e-20)
 
 
-def mixture(h, w, p, f):
-    """The routed feed-forward: the last ``identity`` router outputs stand for experts that return their input."""
+def choice_margin(h, w, p, router):
+    """Per token, by how much a router logit would have to move for the last chosen expert and the best one not
+    chosen to change places (infinite when all are chosen): the gap of their choice scores over the sum of their
+    plain scores, since a logit's change of d moves a score s by about s d."""
+    scores = torch.softmax(h @ w[p + "router"].T, dim=-1)
+    top = int(router["top"])
+    if top >= scores.shape[-1]:
+        return torch.full((h.shape[0],), math.inf, dtype=F64)
+    best, index = torch.sort(scores + w[p + "correction"], dim=-1, descending=True)
+    both = scores.gather(1, index[:, top - 1:top + 1]).sum(dim=-1)
+    return (best[:, top - 1] - best[:, top]) / both
+
+
+def mixture(h, w, p, f, margins=None, forced=None, choices=None):
+    """The routed feed-forward: the last ``identity`` router outputs stand for experts that return their input.
+    ``margins``: a list that receives ``choice_margin`` of this call. ``forced`` [T, top]: experts to use in
+    place of the router's own choice (their weights are still their plain scores over their sum); ``choices``
+    receives the router's own choice all the same."""
     router = f["router"]
     real = int(router["experts"])
     chosen, weights = route(h, w, p, router)
+    if choices is not None:
+        choices.append(chosen)
+    if forced is not None:
+        chosen = torch.as_tensor(forced, dtype=torch.long)
+        picked = torch.gather(torch.softmax(h @ w[p + "router"].T, dim=-1), 1, chosen)
+        weights = picked / (picked.sum(dim=-1, keepdim=True) + 1e-20)
+    if margins is not None:
+        margins.append(choice_margin(h, w, p, router))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, weight in zip(chosen[t].tolist(), weights[t]):
@@ -148,14 +172,17 @@ def to_f64(weights: dict) -> dict:
     return {name: (t.to(F64) if t.is_floating_point() else t) for name, t in weights.items()}
 
 
-def forward(config: dict, weights: dict, tokens, return_layers: bool = False):
-    """Logits [T, vocab] of one whole sequence (and, when asked, the stream after every layer)."""
+def forward(config: dict, weights: dict, tokens, return_layers: bool = False, margins: list | None = None,
+            forced: list | None = None, choices: list | None = None):
+    """Logits [T, vocab] of one whole sequence (and, when asked, the stream after every layer). ``margins``
+    receives every routed layer's ``choice_margin`` and ``choices`` its router's own choice; ``forced`` gives
+    every routed layer's experts, layer by layer (``mixture``)."""
     w = to_f64(weights)
     eps = float(config["norm"]["eps"])
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     x = w["embed"][tokens] * float(config.get("embedding", {}).get("scale", 1.0))
     side = config.get("token_side")
-    taps = []
+    taps, routed = [], 0
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
         if layer["type"] != "attention":
@@ -163,7 +190,9 @@ def forward(config: dict, weights: dict, tokens, return_layers: bool = False):
         mixed = attention(x, w, p + "mix.", layer["mixer"], eps)
         x = x + layer_norm(mixed, w[p + "norm1"], eps) * w[p + "ls1"]
         if layer.get("mlp") is not None:
-            fed = mixture(x, w, p + "mlp.", layer["mlp"])
+            fed = mixture(x, w, p + "mlp.", layer["mlp"], margins, forced[routed] if forced is not None else None,
+                          choices)
+            routed += 1
             x = x + layer_norm(fed, w[p + "norm2"], eps) * w[p + "ls2"]
         if side is not None:
             x = x + token_input(x, tokens, w, i, int(side["dim"]), eps)
