@@ -2,7 +2,8 @@
 // head_dim 128, pages of 16 or 32 slots.
 //
 // Same mathematics and visibility rule as attention.cu / attention_mma.cu (query at p sees key j
-// iff j <= p and (window == 0 or j > p - window); scores q.k * scale; float softmax; query head h
+// iff j <= p and (window == 0 or j > p - window or j < keep: the sequence's first `keep` positions stay in
+// sight under a window); scores q.k * scale; float softmax; query head h
 // reads KV head h / group), cf. app/native/src/mx_attention.c:16-68 and
 // app/architectures/qwen_layers.py:12-17,94-100.
 //
@@ -80,6 +81,7 @@ struct AtParams {
     int* status;
     long long n_pages;
     int out_stride, bt_stride, n_heads, n_kv_heads, group, tokens_per_tile, page_size, page_shift, window;
+    int keep;                    // under a window: keys at positions below this are seen at any distance
     float scale_log2;
     // capped scores: cap_log2 = cap * log2(e) > 0 turns score * scale into cap * tanh(score * scale / cap)
     // (cap_in = scale / cap), already in the units of the exponential; 0: no cap
@@ -247,10 +249,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     const int lo_tile = p.window > 0 ? max(0, ctx + tok0 - p.window + 1) : 0;
     // the tile's chunks of 128 keys, and this block's share of them when the keys are split (few tiles, a
     // long context: the shares are merged by mx_attention_merge_bf16); a share may be empty
-    const int first_chunk = lo_tile / AT_KEYS;
-    const int all_chunks = hi_tile / AT_KEYS + 1 - first_chunk;
+    // With kept first tokens the tile walks two runs of chunks, the kept tokens' and the window's, as one list:
+    // entry i is chunk i below kept_chunks and chunk i + skipped from there on (skipped = the chunks between the
+    // runs, 0 when they touch; without kept tokens kept_chunks is 0 and skipped the window's first chunk).
+    const int kept_chunks = (p.window > 0 && p.keep > 0) ? (p.keep + AT_KEYS - 1) / AT_KEYS : 0;
+    const int skipped = max(0, lo_tile / AT_KEYS - kept_chunks);
+    const int all_chunks = hi_tile / AT_KEYS + 1 - skipped;
     const int per_split = (all_chunks + p.n_splits - 1) / p.n_splits;
-    const int c_begin = first_chunk + (int)blockIdx.z * per_split;
+    const int i_begin = (int)blockIdx.z * per_split;
+    auto chunk_of = [&](int j) { const int i = i_begin + j; return i < kept_chunks ? i : i + skipped; };
     const int n_chunks = max(0, min(per_split, all_chunks - (int)blockIdx.z * per_split));
     if (n_chunks == 0) {                                            // an empty share: tell the merge, touch nothing else
         const int t_in = tid / p.group, h_in = tid - t_in * p.group;
@@ -310,10 +317,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             tma_4d(q_tile + AT_TILE, &q_map, 64, 0, kh, q_start + tok0, &sh.q_full);
         }
         // this tile's part of the block table, read once (entries beyond AT_TABLE stay in global memory)
-        const int first_page = (c_begin * AT_KEYS) >> p.page_shift;
+        auto logical_page = [&](int i) {          // the i-th page of this block's list of chunks
+            const int j = i / pages_per_chunk;
+            return ((chunk_of(j) * AT_KEYS) >> p.page_shift) + (i - j * pages_per_chunk);
+        };
         const int n_table = min(n_chunks * pages_per_chunk, AT_TABLE);
         for (int i = lane; i < n_table; i += 32) {
-            const int lp = first_page + i;
+            const int lp = logical_page(i);
             table[i] = lp < p.bt_stride ? bt[lp] : -1;
         }
         __syncwarp();
@@ -329,13 +339,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                                 : at_wait(&sh.pv_done[before & 1], (unsigned)(before >> 1) & 1, p.status);
             }
             if (!__shfl_sync(0xffffffffu, free_now, 0)) break;
-            const int c0 = (c_begin + j) * AT_KEYS;
+            const int c0 = chunk_of(j) * AT_KEYS;
             long long page = -1;
             if (lane < pages_per_chunk) {
                 const int key0 = c0 + lane * p.page_size;
-                if (key0 <= hi_tile && key0 + p.page_size - 1 >= lo_tile) {
+                if (key0 <= hi_tile && (key0 + p.page_size - 1 >= lo_tile || key0 < p.keep)) {
                     const int i = j * pages_per_chunk + lane;
-                    const int lp = first_page + i;
+                    const int lp = logical_page(i);
                     page = i < AT_TABLE ? table[i] : (lp < p.bt_stride ? bt[lp] : -1);
                     if (page < 0 || page >= p.n_pages) {
                         page = -1;
@@ -464,7 +474,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             pv_consumed_through(j - 1);               // long completed: this only keeps the count in step
             alive = __all_sync(0xffffffffu, alive);   // the tensor-memory accesses below are warp-wide
             if (!alive) *reinterpret_cast<volatile int*>(&sh.abort) = 1;
-            const int c0 = (c_begin + j) * AT_KEYS, k0 = c0 + 64 * part;
+            const int c0 = chunk_of(j) * AT_KEYS, k0 = c0 + 64 * part;
             // rows that belong to no token of the tile need no mask: whatever they compute is never stored,
             // and a row's output depends on that row alone
             const bool edge = __any_sync(0xffffffffu, valid && (k0 + 63 > pos || k0 < lo));
@@ -496,7 +506,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 #pragma unroll
                     for (int c = 0; c < 64; ++c) {
                         const int key = k0 + c;
-                        sc[c] = (key <= pos && key >= lo) ? sc[c] : -INFINITY;
+                        sc[c] = (key <= pos && (key >= lo || key < p.keep)) ? sc[c] : -INFINITY;
                     }
                 }
                 // four chains, so that the maximum is not one chain of 64 dependent instructions
@@ -685,7 +695,7 @@ extern "C" int mx_paged_attention_tc_split(const void* q, int q_stride, const vo
                                            const int* context_lens, const int* tiles, int n_tiles, int n_tokens,
                                            int n_heads, int n_kv_heads, int head_dim, int window, float scale,
                                            void* out, int out_stride, int n_splits, float* scratch, int* status,
-                                           float softcap, const float* sink, cudaStream_t stream) {
+                                           float softcap, const float* sink, int keep_first, cudaStream_t stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return MX_OK;
     if (n_splits < 1 || n_splits > 64) MX_REFUSE("tcgen05 attention: %d key splits", n_splits);
     if (n_splits > 1 && scratch == nullptr) MX_REFUSE("tcgen05 attention: key splits without scratch memory");
@@ -732,7 +742,7 @@ extern "C" int mx_paged_attention_tc_split(const void* q, int q_stride, const vo
     p.out = (__nv_bfloat16*)out; p.status = status; p.n_pages = n_pages; p.out_stride = out_stride;
     p.bt_stride = bt_stride; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.group = group;
     p.tokens_per_tile = tokens_per_tile; p.page_size = page_size; p.page_shift = page_size == 16 ? 4 : 5;
-    p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    p.window = window; p.keep = window > 0 ? max(keep_first, 0) : 0; p.scale_log2 = scale * 1.4426950408889634f;
     p.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
     p.sink = sink;
@@ -760,5 +770,5 @@ extern "C" int mx_paged_attention_tc(const void* q, int q_stride, const void* ca
                                      void* out, int out_stride, int* status, cudaStream_t stream) {
     return mx_paged_attention_tc_split(q, q_stride, cache, n_pages, page_size, block_tables, bt_stride, cu_q,
                                        context_lens, tiles, n_tiles, n_tokens, n_heads, n_kv_heads, head_dim, window,
-                                       scale, out, out_stride, 1, nullptr, status, 0.f, nullptr, stream);
+                                       scale, out, out_stride, 1, nullptr, status, 0.f, nullptr, 0, stream);
 }

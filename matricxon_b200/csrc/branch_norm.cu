@@ -6,6 +6,9 @@
 //   row held in registers (rows that are no multiple of 4 or too long: in shared memory). `scale` (a vector, may be
 //   null) is the layer's learned scale of the branch. `act` (may be null) receives the new x in bfloat16 or float:
 //   the next sublayer's input, so that no rounding pass follows.
+//   `centre` 0 leaves the mean in: x[r] += y / sqrt(mean(y^2) + eps) * weight, the root-mean-square form.
+// mx_gelu_gate_rows: g[t][d] = gelu_tanh(z[t][d]) * table[token id][col0 + d], the middle of the token input when its
+//   two products run as matrix products (wide layers); mx_token_side_input is the whole of it in one kernel.
 // mx_scale_rows: x *= s (the constant some models put on their logits).
 // mx_token_side_input: per token t and layer, with e = table[token id][col0 .. col0 + dim):
 //     g = gelu_tanh(G x_t) * e            G [dim][hidden]
@@ -26,7 +29,7 @@ template <typename TAct, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 layernorm_scaled_add_vec_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ weight,
                                 const float* __restrict__ bias, const float* __restrict__ scale, TAct* __restrict__ act,
-                                int hidden, float eps) {
+                                int hidden, float eps, int centre) {
     __shared__ float scratch[32];
     const int r = blockIdx.x, n_vec = hidden >> 2;
     const float4* yr = reinterpret_cast<const float4*>(y + (size_t)r * hidden);
@@ -38,7 +41,7 @@ layernorm_scaled_add_vec_kernel(float* __restrict__ x, const float* __restrict__
         v[j] = i < n_vec ? yr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
     }
-    const float mean = block_sum(s, scratch) / (float)hidden;
+    const float mean = centre ? block_sum(s, scratch) / (float)hidden : 0.f;
     float q = 0.f;
 #pragma unroll
     for (int j = 0; j < BN_VPT; ++j) {
@@ -79,7 +82,7 @@ template <typename TAct>
 __global__ void layernorm_scaled_add_kernel(float* __restrict__ x, const float* __restrict__ y,
                                             const float* __restrict__ weight, const float* __restrict__ bias,
                                             const float* __restrict__ scale, TAct* __restrict__ act, int hidden,
-                                            float eps) {
+                                            float eps, int centre) {
     extern __shared__ float row_cache[];
     __shared__ float scratch[32];
     const int r = blockIdx.x;
@@ -90,7 +93,7 @@ __global__ void layernorm_scaled_add_kernel(float* __restrict__ x, const float* 
         row_cache[i] = v;
         s += v;
     }
-    const float mean = block_sum(s, scratch) / (float)hidden;
+    const float mean = centre ? block_sum(s, scratch) / (float)hidden : 0.f;
     float q = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         const float d = row_cache[i] - mean;
@@ -110,6 +113,21 @@ __global__ void layernorm_scaled_add_kernel(float* __restrict__ x, const float* 
 __global__ void scale_rows_kernel(float* __restrict__ x, long long count, float s) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < count) x[i] *= s;
+}
+
+// out[t][d] = gelu_tanh(z[t][d]) * table[id_t][col0 + d]: what the token brings, gated by the stream's projection
+template <typename T>
+__global__ void gelu_gate_rows_kernel(const float* __restrict__ z, int ld, const int* __restrict__ token_ids,
+                                      const T* __restrict__ table, int table_ld, int col0, int vocab, T* __restrict__ out,
+                                      int n_tokens, int dim, int* status) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_tokens * dim) return;
+    const int t = (int)(i / dim), d = (int)(i - (long long)t * dim);
+    const int id = token_ids[t];
+    float e = 0.f;
+    if (id >= 0 && id < vocab) e = to_float(table[(size_t)id * table_ld + col0 + d]);
+    else if (d == 0) atomicOr(status, MX_STATUS_BAD_TOKEN_ID);
+    out[i] = from_float<T>(gelu_tanh(z[(size_t)t * ld + d]) * e);
 }
 
 constexpr int TS_TOKENS = 4;       // tokens a block handles together
@@ -195,18 +213,18 @@ token_side_input_kernel(float* __restrict__ x, TAct* __restrict__ act, const int
 
 extern "C" int mx_layernorm_scaled_add(float* x, const float* y, const float* weight, const float* bias,
                                        const float* scale, void* act, int act_dtype, int n_rows, int hidden, float eps,
-                                       cudaStream_t stream) {
+                                       int centre, cudaStream_t stream) {
     if (n_rows <= 0 || hidden <= 0) return MX_OK;
     const bool aligned = (((uintptr_t)x | (uintptr_t)y | (uintptr_t)weight | (uintptr_t)bias | (uintptr_t)scale) & 15) == 0;
     const bool f32 = act_dtype == MX_DTYPE_F32;
     if (hidden % 4 == 0 && aligned && hidden <= 4 * BN_VPT * 512) {
         const int n_vec = hidden / 4;
         if (n_vec <= BN_VPT * 128) {
-            if (f32) layernorm_scaled_add_vec_kernel<float, 128><<<n_rows, 128, 0, stream>>>(x, y, weight, bias, scale, (float*)act, hidden, eps);
-            else layernorm_scaled_add_vec_kernel<__nv_bfloat16, 128><<<n_rows, 128, 0, stream>>>(x, y, weight, bias, scale, (__nv_bfloat16*)act, hidden, eps);
+            if (f32) layernorm_scaled_add_vec_kernel<float, 128><<<n_rows, 128, 0, stream>>>(x, y, weight, bias, scale, (float*)act, hidden, eps, centre);
+            else layernorm_scaled_add_vec_kernel<__nv_bfloat16, 128><<<n_rows, 128, 0, stream>>>(x, y, weight, bias, scale, (__nv_bfloat16*)act, hidden, eps, centre);
         } else {
-            if (f32) layernorm_scaled_add_vec_kernel<float, 512><<<n_rows, 512, 0, stream>>>(x, y, weight, bias, scale, (float*)act, hidden, eps);
-            else layernorm_scaled_add_vec_kernel<__nv_bfloat16, 512><<<n_rows, 512, 0, stream>>>(x, y, weight, bias, scale, (__nv_bfloat16*)act, hidden, eps);
+            if (f32) layernorm_scaled_add_vec_kernel<float, 512><<<n_rows, 512, 0, stream>>>(x, y, weight, bias, scale, (float*)act, hidden, eps, centre);
+            else layernorm_scaled_add_vec_kernel<__nv_bfloat16, 512><<<n_rows, 512, 0, stream>>>(x, y, weight, bias, scale, (__nv_bfloat16*)act, hidden, eps, centre);
         }
         return mx_launch_status();
     }
@@ -215,11 +233,11 @@ extern "C" int mx_layernorm_scaled_add(float* x, const float* y, const float* we
     if (f32) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(layernorm_scaled_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        layernorm_scaled_add_kernel<float><<<n_rows, 256, smem, stream>>>(x, y, weight, bias, scale, (float*)act, hidden, eps);
+        layernorm_scaled_add_kernel<float><<<n_rows, 256, smem, stream>>>(x, y, weight, bias, scale, (float*)act, hidden, eps, centre);
     } else {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(layernorm_scaled_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        layernorm_scaled_add_kernel<__nv_bfloat16><<<n_rows, 256, smem, stream>>>(x, y, weight, bias, scale, (__nv_bfloat16*)act, hidden, eps);
+        layernorm_scaled_add_kernel<__nv_bfloat16><<<n_rows, 256, smem, stream>>>(x, y, weight, bias, scale, (__nv_bfloat16*)act, hidden, eps, centre);
     }
     return mx_launch_status();
 }
@@ -243,6 +261,24 @@ static int launch_token_side(float* x, void* act, const int* token_ids, const vo
     token_side_input_kernel<T, TAct><<<(n_tokens + TS_TOKENS - 1) / TS_TOKENS, threads, smem, stream>>>(
         x, (TAct*)act, token_ids, (const T*)table, table_ld, col0, vocab, (const T*)gate, (const T*)proj, norm, n_tokens,
         hidden, dim, eps, status);
+    return mx_launch_status();
+}
+
+// `dtype` is the type of table and out.
+extern "C" int mx_gelu_gate_rows(const float* z, int ld, const int* token_ids, const void* table, int table_ld, int col0,
+                                 int vocab, void* out, int dtype, int n_tokens, int dim, int* status,
+                                 cudaStream_t stream) {
+    if (n_tokens <= 0) return MX_OK;
+    if (dim <= 0 || col0 < 0 || col0 + dim > table_ld || ld < dim) MX_REFUSE("token input: columns %d..%d of a table of %d", col0, col0 + dim, table_ld);
+    const long long count = (long long)n_tokens * dim;
+    const unsigned blocks = (unsigned)((count + 255) / 256);
+    if (dtype == MX_DTYPE_F32)
+        gelu_gate_rows_kernel<float><<<blocks, 256, 0, stream>>>(z, ld, token_ids, (const float*)table, table_ld, col0, vocab,
+                                                                 (float*)out, n_tokens, dim, status);
+    else
+        gelu_gate_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(z, ld, token_ids, (const __nv_bfloat16*)table,
+                                                                         table_ld, col0, vocab, (__nv_bfloat16*)out,
+                                                                         n_tokens, dim, status);
     return mx_launch_status();
 }
 

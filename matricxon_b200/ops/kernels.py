@@ -448,8 +448,9 @@ def paged_attention_tc(q: torch.Tensor, q_stride: int, cache: torch.Tensor, bloc
                        n_tokens: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int | None,
                        scale: float, out: torch.Tensor, status: torch.Tensor, n_splits: int = 1,
                        scratch: torch.Tensor | None = None, softcap: float | None = None,
-                       sink: torch.Tensor | None = None) -> None:
-    """Attention of prompt portions on tcgen05 (bfloat16, head_dim 128, pages of 16 or 32).
+                       sink: torch.Tensor | None = None, keep_first: int = 0) -> None:
+    """Attention of prompt portions on tcgen05 (bfloat16, head_dim 128, pages of 16 or 32). Under a window the
+    sequence's first ``keep_first`` keys stay visible.
     ``tiles`` is int32 [n_tiles, 2]: (sequence, first token) of tiles of 128 // group tokens
     (``attention_tile_lists(..., token_tiles=True)``); ``q`` holds the step's rows, query head h
     at column h * head_dim. ``n_splits`` > 1 shares every tile's keys out between that many blocks
@@ -472,7 +473,7 @@ def paged_attention_tc(q: torch.Tensor, q_stride: int, cache: torch.Tensor, bloc
         block_tables.stride(0), _ptr(cu_q), _ptr(context_lens), _ptr(tiles), n_tiles, n_tokens,
         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(out), out.stride(0),
         int(n_splits), _ptr(scratch) if n_splits > 1 else None, _ptr(status), float(softcap or 0.0),
-        _sink_ptr(sink, n_heads), _stream()), "paged_attention_tc")
+        _sink_ptr(sink, n_heads), int(keep_first) if window else 0, _stream()), "paged_attention_tc")
     _launched()
 
 
@@ -1210,9 +1211,11 @@ def moe_combine_sorted(rows: torch.Tensor, ids: torch.Tensor, place: torch.Tenso
 
 # ---------------------------------------------------------------------- branches normalised on their way out
 def layernorm_scaled_add(x: torch.Tensor, branch: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
-                         scale: torch.Tensor | None, eps: float, act: torch.Tensor | None = None) -> None:
+                         scale: torch.Tensor | None, eps: float, act: torch.Tensor | None = None,
+                         centre: bool = True) -> None:
     """x[r] += LayerNorm(branch[r]) * weight (+ bias), times ``scale`` entry by entry (a float32 vector or None); float
-    statistics. ``act`` (bfloat16 or float32, same shape) receives the new rows."""
+    statistics. ``act`` (bfloat16 or float32, same shape) receives the new rows. ``centre`` False leaves the mean in:
+    the branch is divided by its root mean square."""
     _need(x, "x", torch.float32)
     _need(branch, "branch", torch.float32)
     _need(weight, "weight", torch.float32)
@@ -1227,7 +1230,7 @@ def layernorm_scaled_add(x: torch.Tensor, branch: torch.Tensor, weight: torch.Te
         assert tuple(act.shape) == (n, hidden)
     check(library().mx_layernorm_scaled_add(_ptr(x), _ptr(branch), _ptr(weight), _ptr(bias), _ptr(scale), _ptr(act),
                                             dtype_code(act.dtype) if act is not None else F32, n, hidden, float(eps),
-                                            _stream()), "layernorm_scaled_add")
+                                            1 if centre else 0, _stream()), "layernorm_scaled_add")
     _launched()
 
 
@@ -1261,6 +1264,23 @@ def token_side_input(x: torch.Tensor, token_ids: torch.Tensor, table: torch.Tens
     check(library().mx_token_side_input(_ptr(x), _ptr(act), _ptr(token_ids), _ptr(table), table.shape[1], int(column),
                                         table.shape[0], _ptr(gate), _ptr(proj), _ptr(norm), dtype_code(table.dtype), n,
                                         hidden, dim, float(eps), _ptr(status), _stream()), "token_side_input")
+    _launched()
+
+
+def gelu_gate_rows(z: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, column: int, out: torch.Tensor,
+                   status: torch.Tensor) -> None:
+    """out[t] = gelu_tanh(z[t]) * table[id_t, column:column + dim]: ``z`` float32 [tokens, dim], ``out`` [tokens, dim]
+    in the table's dtype."""
+    _need(z, "z", torch.float32, contiguous=False)
+    _need(token_ids, "token_ids", torch.int32)
+    _need(table, "table")
+    _need(out, "out", table.dtype)
+    _need(status, "status", torch.int32)
+    n, dim = out.shape
+    assert tuple(z.shape) == (n, dim) and z.stride(1) == 1 and token_ids.numel() >= n
+    check(library().mx_gelu_gate_rows(_ptr(z), z.stride(0), _ptr(token_ids), _ptr(table), table.shape[1], int(column),
+                                      table.shape[0], _ptr(out), dtype_code(table.dtype), n, dim, _ptr(status), _stream()),
+          "gelu_gate_rows")
     _launched()
 
 

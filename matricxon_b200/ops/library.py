@@ -43,7 +43,7 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_attention_scratch_bytes": ([I, I, I, I], L),
     "mx_paged_attention_mma": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, I, I, P, P, F, P, I, P], I),
     "mx_paged_attention_tc": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, F, P, I, P, P], I),
-    "mx_paged_attention_tc_split": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, F, P, I, I, P, P, F, P, P], I),
+    "mx_paged_attention_tc_split": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, F, P, I, I, P, P, F, P, I, P], I),
     "mx_paged_attention": ([P, I, I, P, L, I, P, I, P, P, I, I, I, I, I, F, P, I, I, P, P, F, P, I, P], I),
     "mx_rmsnorm": ([P, P, P, F, P, I, I, I, F, P], I),
     "mx_rmsnorm_sum": ([P, P, F, P, F, P, I, I, I, F, P], I),
@@ -74,7 +74,8 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_moe_gemm": ([P, I, I, P, I, P, L, I, I, P, P, I, P, P, I, I, F, F, F, P], I),
     "mx_moe_combine": ([P, P, I, I, I, P, P, P, I, I, I, P], I),
     "mx_rotate_norm_kv_write": ([P, I, P, P, I, F, P, P, L, I, P, I, I, I, I, I, I, I, P, P], I),
-    "mx_layernorm_scaled_add": ([P, P, P, P, P, P, I, I, I, F, P], I),
+    "mx_layernorm_scaled_add": ([P, P, P, P, P, P, I, I, I, F, I, P], I),
+    "mx_gelu_gate_rows": ([P, I, P, P, I, I, I, P, I, I, I, P, P], I),
     "mx_scale_rows": ([P, L, F, P], I),
     "mx_token_side_input": ([P, P, P, P, I, I, I, P, P, P, I, I, I, I, F, P, P], I),
     "mx_glu": ([P, I, P, I, I, I, I, P], I),

@@ -106,8 +106,8 @@ def paged_attend(q, q_stride, ctx, binding, rt, n_heads, n_kv_heads, head_dim, w
     tiles and the key splits for this step. Returns [tokens, heads * head_dim] in the runtime dtype.
     ``softcap`` caps the scaled scores at ``softcap * tanh(score / softcap)``; ``sink`` (float32, one logit per
     head) joins the softmax's denominator without a value. ``keep_first``: under a window, the keys of the
-    sequence's first ``keep_first`` positions stay visible at any distance. Every kernel takes cap and sink; the
-    tcgen05 kernel walks one unbroken run of keys, so windows with kept first tokens go to the mma.sync tiles."""
+    sequence's first ``keep_first`` positions stay visible at any distance. Every kernel takes cap, sink and kept
+    tokens."""
     keep_first = int(keep_first) if window is not None else 0
     extras = {"softcap": softcap, "sink": sink}
     kept = {"keep_first": keep_first}
@@ -118,8 +118,7 @@ def paged_attend(q, q_stride, ctx, binding, rt, n_heads, n_kv_heads, head_dim, w
     if kernels.mma_attention_supported(rt.dtype, head_dim, rt.page_size, q_stride):
         group_size = n_heads // n_kv_heads
         # prompt portions on tcgen05 when the kernel takes the geometry, else on mma.sync
-        on_tc = _TC_ATTENTION and keep_first == 0 and kernels.tc_attention_supported(
-            rt.dtype, head_dim, rt.page_size, q_stride, group_size)
+        on_tc = _TC_ATTENTION and kernels.tc_attention_supported(rt.dtype, head_dim, rt.page_size, q_stride, group_size)
         narrow, n_narrow, wide, n_wide = attention_tiles(ctx, group_size, token_tiles=on_tc)
         for tiles, n_tiles, is_narrow in ((narrow, n_narrow, True), (wide, n_wide, False)):
             if n_tiles == 0:
@@ -131,7 +130,7 @@ def paged_attend(q, q_stride, ctx, binding, rt, n_heads, n_kv_heads, head_dim, w
                                            ctx.context_lens, tiles, n_tiles, ctx.n_tokens,
                                            n_heads, n_kv_heads, head_dim,
                                            window, scale, attn, ctx.status,
-                                           n_splits=n_splits, scratch=scratch, **extras)
+                                           n_splits=n_splits, scratch=scratch, **extras, **kept)
                 continue
             alone = (n_wide == 0) if is_narrow else (n_narrow == 0)
             if is_narrow and ctx.padded:

@@ -16,7 +16,7 @@ Interfaces (duck-typed; these base classes state them):
   Mixer.forward(h, residual, ctx, binding) -> residual + mix(h)      (float32)
   Mixer.cache_request(spec) / Mixer.state_request(spec): what the cache manager must hold.
   FeedForward.forward(h, residual, ctx) -> residual + ffn(h)          (float32)
-  SideInput.forward(x, ctx) -> (x, activations)                        (x updated in place)
+  SideInput.forward(x, h, ctx) -> (x, activations)                     (x updated in place; h = x in the runtime dtype)
   Block.forward(x, ctx, binding) -> x                                  (float32)
 """
 
@@ -180,10 +180,11 @@ class FeedForward(Part):
 
 
 class SideInput(Part):
-    """Something a layer adds to the residual stream after its sublayers. ``forward(x, ctx)`` updates the float
-    stream in place and returns (x, activations): the new rows in the runtime dtype (x itself in float32)."""
+    """Something a layer adds to the residual stream after its sublayers. ``forward(x, h, ctx)`` (``h``: the rows of
+    ``x`` in the runtime dtype) updates the float stream in place and returns (x, activations): the new rows in the
+    runtime dtype (x itself in float32)."""
 
-    def forward(self, x, ctx):
+    def forward(self, x, h, ctx):
         raise NotImplementedError
 
 

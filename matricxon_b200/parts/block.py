@@ -226,7 +226,7 @@ class BranchNormSequentialBlock(Block):
             fed = self.feed_forward.forward(h, None, ctx)
             x, h = self.ffn_norm.forward_scaled_add(x, fed, self.ffn_scale)
         if self.side_input is not None:
-            x, h = self.side_input.forward(x, ctx)
+            x, h = self.side_input.forward(x, h, ctx)
         ctx.memo["stream_activations"] = (x, h)
         return x
 
