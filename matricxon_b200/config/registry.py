@@ -117,6 +117,14 @@ def _register_builtin() -> None:
         config_class=BafusunConfig,
         build_model=_build_decoder,
     ))
+    from matricxon_b200.config.kefasun import KefasunConfig
+
+    register_architecture(ArchitectureEntry(
+        name="Kefasun",
+        aliases=("kefasun",),
+        config_class=KefasunConfig,
+        build_model=_build_decoder,
+    ))
 
 
 _register_builtin()

@@ -110,7 +110,7 @@ paged_attention_kernel(const AttnParams p) {
     }
     const int pos = p.positions[t];
     const int hi = pos;
-    const int lo = (p.window > 0) ? max(0, pos - p.window + 1) : 0;
+    const int lo = first_visible_key(pos, p.window);
     // keys [0, kept) are seen beside [lo, hi]; their chunks that lie wholly before the window's first chunk are
     // walked first: the walk counts v = 0 .. n_chunks - 1, chunk v for v < n_kept, else first_chunk + v - n_kept
     const int kept = lo > 0 ? min(p.keep_first, lo) : 0;

@@ -241,16 +241,16 @@ attention_mma_kernel(const MmaAttnParams p) {
         r_tok[i] = rr / group;
         r_head[i] = rr - r_tok[i] * group;
         r_pos[i] = ctx + r_tok[i];
-        r_lo[i] = p.window > 0 ? max(0, r_pos[i] - p.window + 1) : 0;
+        r_lo[i] = first_visible_key(r_pos[i], p.window);
     }
     // key range of the block (what is fetched) and of the warp (what it computes)
     const int hi_tile = ctx + tile_last / group;
-    const int lo_tile = p.window > 0 ? max(0, ctx + tile_row0 / group - p.window + 1) : 0;
+    const int lo_tile = first_visible_key(ctx + tile_row0 / group, p.window);
     const int hi_warp = warp_has_rows ? ctx + last_row / group : -1;
-    const int lo_warp = p.window > 0 ? max(0, ctx + row0 / group - p.window + 1) : 0;
+    const int lo_warp = first_visible_key(ctx + row0 / group, p.window);
     // rows of the warp see every key of a chunk that lies in [all_lo, all_hi]: no mask needed
     const int all_hi = warp_has_rows ? ctx + row0 / group : -1;
-    const int all_lo = p.window > 0 ? max(0, hi_warp - p.window + 1) : 0;
+    const int all_lo = first_visible_key(hi_warp, p.window);
     const bool rows_full = row0 + 15 < n_rows;
     // keys [0, kept) are seen beside the window's: their chunks that lie wholly before the window's first one
     // are walked first. The walk counts v = 0 .. n_chunks - 1: chunk v for v < n_kept, then the window's chunks.

@@ -246,7 +246,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     const int n_tok = min(p.tokens_per_tile, q_len - tok0);
     if (n_tok <= 0) return;                                         // nothing was allocated yet
     const int hi_tile = ctx + tok0 + n_tok - 1;
-    const int lo_tile = p.window > 0 ? max(0, ctx + tok0 - p.window + 1) : 0;
+    const int lo_tile = first_visible_key(ctx + tok0, p.window);
     // the tile's chunks of 128 keys, and this block's share of them when the keys are split (few tiles, a
     // long context: the shares are merged by mx_attention_merge_bf16); a share may be empty
     // With kept first tokens the tile walks two runs of chunks, the kept tokens' and the window's, as one list:
@@ -451,7 +451,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         const int t_in = row / p.group, h_in = row - t_in * p.group;
         const bool valid = row < p.tokens_per_tile * p.group && t_in < n_tok;
         const int pos = valid ? ctx + tok0 + t_in : -1;                 // -1: every key is masked
-        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const int lo = first_visible_key(pos, p.window);
         const unsigned lane_base = (unsigned)(32 * (warp & 3)) << 16;
         float m_ref = -INFINITY, l_run = 0.f;
         bool alive = true;

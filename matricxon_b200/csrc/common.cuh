@@ -81,6 +81,16 @@ static inline cudaError_t mx_launch_chained(void (*kernel)(KArgs...), dim3 grid,
     return cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
 }
 
+// The first key position that a query at `pos` may see, by the attention kernels' one mask parameter:
+// window > 0: the last `window` positions (pos - window + 1, not below 0); window < 0: the start of the query's
+// own block of -window positions, blocks counted from position 0 of the sequence (keys of earlier blocks are
+// out of sight however near); 0: every earlier position. It never decreases with `pos`.
+__device__ __forceinline__ int first_visible_key(int pos, int window) {
+    if (window > 0) return max(0, pos - window + 1);
+    if (window < 0) return pos >= 0 ? pos - pos % (-window) : 0;
+    return 0;
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -13,13 +13,15 @@
 //   q_plain [tokens][heads * dim]          (activation dtype: the batched product's operand)
 //   q_lat   [tokens][heads][Dk]            the rotated query part at offset rank
 //   cache   [slot][Dk]                     unit(latent) * weight, then the rotated shared part
-// Rotation: of the `rot` elements the first rot_dims are rotated, pair (i, i + rot_dims/2), by the
+// (the latent and the shared part may also come from rows of their own, `kvd`).
+// Rotation: of the `rot` elements the first rot_dims are rotated, pair (i, i + rot_dims/2) or, `interleaved`, (2i, 2i + 1), by the
 // angle position * freq[i] (float), cos and sin times `amplitude`; the rest pass unchanged.
 //
 // mx_latent_attention: one block per (token, group of up to LAT_HEADS heads). Keys are walked in
 // chunks of 32 positions (one key per lane) from max(0, p - window + 1) to p; scores, the running
 // softmax and the weighted sum are float. A query at position p sees key j iff j <= p and
-// (window == 0 or j > p - window).
+// (window == 0 or j > p - window; window < 0: j in the query's own block of -window positions). A sink (one
+// logit per head, or none) joins the softmax's denominator without a value.
 #include <math.h>
 
 #include "common.cuh"
@@ -32,9 +34,23 @@ constexpr int LAT_HEADS = 8;      // heads per block at most
 constexpr int LAT_KEYS = 32;
 constexpr int LAT_PREP_HEADS = 4;  // query heads per block of the preparing kernel
 
+// Entry d of a vector whose first rot_dims entries are rotated: pair i is (i, i + half) or, interleaved,
+// (2i, 2i + 1); cs holds cos[half] then sin[half] of the pairs' angles.
+__device__ __forceinline__ float rotated_entry(const float* src, int d, int half, int rot_dims, int interleaved,
+                                               const float* cs) {
+    if (d >= rot_dims) return src[d];
+    if (interleaved) {
+        const int i = d >> 1;
+        return (d & 1) ? src[d] * cs[i] + src[d - 1] * cs[half + i] : src[d] * cs[i] - src[d + 1] * cs[half + i];
+    }
+    if (d < half) return src[d] * cs[d] - src[d + half] * cs[half + d];
+    return src[d] * cs[d - half] + src[d - half] * cs[d];
+}
+
 template <typename T>
 __global__ void __launch_bounds__(LAT_THREADS)
-latent_prepare_kernel(const float* __restrict__ qd, int ld, const int* __restrict__ positions,
+latent_prepare_kernel(const float* __restrict__ qd, int ld, const float* __restrict__ kvd, int ld_kv, int interleaved,
+                      const int* __restrict__ positions,
                       const float* __restrict__ freq, float amplitude, const float* __restrict__ latent_weight,
                       float eps, const int* __restrict__ slots, T* __restrict__ cache, long long n_slots,
                       T* __restrict__ q_plain, T* __restrict__ q_lat, int n_heads, int dim, int rot,
@@ -66,10 +82,7 @@ latent_prepare_kernel(const float* __restrict__ qd, int ld, const int* __restric
             // the rotated part, to the tail of the head's latent-space query
             src += dim;
             for (int d = threadIdx.x; d < rot; d += blockDim.x) {
-                float v;
-                if (d < half) v = src[d] * cs[d] - src[d + half] * cs[half + d];
-                else if (d < rot_dims) v = src[d] * cs[d - half] + src[d - half] * cs[d];
-                else v = src[d];
+                const float v = rotated_entry(src, d, half, rot_dims, interleaved, cs);
                 q_lat[((size_t)t * n_heads + h) * dk + rank + d] = from_float<T>(v);
             }
         }
@@ -77,7 +90,8 @@ latent_prepare_kernel(const float* __restrict__ qd, int ld, const int* __restric
     }
     // block 0 of a token: its cache vector
     const long long slot = slots ? slots[t] : -1;
-    const float* lat = row + (size_t)n_heads * qw;
+    // the latent and the shared rotated part follow the query heads, or lie in rows of their own
+    const float* lat = kvd ? after_wait(kvd) + (size_t)t * ld_kv : row + (size_t)n_heads * qw;
     float s = 0.f;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) s = fmaf(lat[i], lat[i], s);
     const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)rank + eps);
@@ -90,10 +104,7 @@ latent_prepare_kernel(const float* __restrict__ qd, int ld, const int* __restric
     for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_float<T>(lat[i] * inv * latent_weight[i]);
     const float* src = lat + rank;
     for (int d = threadIdx.x; d < rot; d += blockDim.x) {
-        float v;
-        if (d < half) v = src[d] * cs[d] - src[d + half] * cs[half + d];
-        else if (d < rot_dims) v = src[d] * cs[d - half] + src[d - half] * cs[d];
-        else v = src[d];
+        const float v = rotated_entry(src, d, half, rot_dims, interleaved, cs);
         dst[rank + d] = from_float<T>(v);
     }
 }
@@ -105,6 +116,7 @@ struct LatentParams {
     const int* block_tables;
     const int* tok_seq;
     const int* positions;
+    const float* sink;        // [n_heads] or null: exp(sink[h]) joins the softmax's denominator, with no value
     int* status;
     long long n_pages;
     int bt_stride, n_heads, rank, dk, page_size, window;
@@ -134,7 +146,7 @@ latent_attention_kernel(const LatentParams p) {
         return;
     }
     const int pos = p.positions[t];
-    const int lo = (p.window > 0) ? max(0, pos - p.window + 1) : 0;
+    const int lo = first_visible_key(pos, p.window);
     const T* qrow = reinterpret_cast<const T*>(p.q) + ((size_t)t * p.n_heads + head0) * dk;
     for (int i = tid; i < gc * dk; i += LAT_THREADS) q_s[i] = to_float(qrow[i]) * p.scale;
 
@@ -208,7 +220,8 @@ latent_attention_kernel(const LatentParams p) {
 #pragma unroll
     for (int hs = 0; hs < HPW; ++hs) {
         const int h = warp + hs * LAT_WARPS;
-        if (h < gc && lane == 0) l_s[h] = l_run[hs];
+        // the sink counts once in the denominator and brings no value
+        if (h < gc && lane == 0) l_s[h] = l_run[hs] + (p.sink ? expf(p.sink[head0 + h] - m_run[hs]) : 0.f);
     }
     __syncthreads();
 #pragma unroll
@@ -234,7 +247,7 @@ int launch_latent(const LatentParams& p, int n_tokens, size_t smem, cudaStream_t
 
 }  // namespace
 
-extern "C" int mx_latent_prepare(const float* qd, int ld, const int* positions, const float* freq,
+extern "C" int mx_latent_prepare(const float* qd, int ld, const float* kvd, int ld_kv, int interleaved, const int* positions, const float* freq,
                                  float amplitude, const float* latent_weight, float eps, const int* slots,
                                  void* cache, long long n_pages, int page_size, void* q_plain, void* q_lat,
                                  int dtype, int n_tokens, int n_heads, int dim, int rot, int rot_dims, int rank,
@@ -242,17 +255,17 @@ extern "C" int mx_latent_prepare(const float* qd, int ld, const int* positions, 
     if (n_tokens <= 0) return MX_OK;
     if (rot_dims < 0 || rot_dims > rot || (rot_dims & 1))
         MX_REFUSE("latent attention: %d rotated dimensions of %d", rot_dims, rot);
-    if (ld < n_heads * (dim + rot) + rank + rot) MX_REFUSE("latent attention: projection rows are too short");
+    if (ld < n_heads * (dim + rot) + (kvd ? 0 : rank + rot) || (kvd && ld_kv < rank + rot)) MX_REFUSE("latent attention: projection rows are too short");
     const size_t smem = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
     const long long n_slots = n_pages * page_size;
     const dim3 grid(n_tokens, 1 + (n_heads + LAT_PREP_HEADS - 1) / LAT_PREP_HEADS);
     if (dtype == MX_DTYPE_F32)
         mx_launch_chained(latent_prepare_kernel<float>, grid, dim3(LAT_THREADS), smem, stream,
-            qd, ld, positions, freq, amplitude, latent_weight, eps, cache ? slots : nullptr, (float*)cache, n_slots,
+            qd, ld, kvd, ld_kv, interleaved, positions, freq, amplitude, latent_weight, eps, cache ? slots : nullptr, (float*)cache, n_slots,
             (float*)q_plain, (float*)q_lat, n_heads, dim, rot, rot_dims, rank, status);
     else
         mx_launch_chained(latent_prepare_kernel<__nv_bfloat16>, grid, dim3(LAT_THREADS), smem, stream,
-            qd, ld, positions, freq, amplitude, latent_weight, eps, cache ? slots : nullptr, (__nv_bfloat16*)cache,
+            qd, ld, kvd, ld_kv, interleaved, positions, freq, amplitude, latent_weight, eps, cache ? slots : nullptr, (__nv_bfloat16*)cache,
             n_slots, (__nv_bfloat16*)q_plain, (__nv_bfloat16*)q_lat, n_heads, dim, rot, rot_dims, rank, status);
     return mx_launch_status();
 }
@@ -260,13 +273,13 @@ extern "C" int mx_latent_prepare(const float* qd, int ld, const int* positions, 
 extern "C" int mx_latent_attention(const void* q, const void* cache, int dtype, long long n_pages, int page_size,
                                    const int* block_tables, int bt_stride, const int* tok_seq,
                                    const int* positions, int n_tokens, int n_heads, int rank, int dk, int window,
-                                   float scale, void* out, int* status, cudaStream_t stream) {
+                                   float scale, void* out, const float* sink, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return MX_OK;
     if (rank <= 0 || dk < rank) MX_REFUSE("latent attention: rank %d of a key of %d", rank, dk);
     if (rank > 8 * LAT_THREADS) MX_REFUSE("latent attention: a latent of %d exceeds %d", rank, 8 * LAT_THREADS);
     LatentParams p;
     p.q = q; p.cache = cache; p.out = out; p.block_tables = block_tables; p.tok_seq = tok_seq;
-    p.positions = positions; p.status = status; p.n_pages = n_pages; p.bt_stride = bt_stride;
+    p.positions = positions; p.sink = sink; p.status = status; p.n_pages = n_pages; p.bt_stride = bt_stride;
     p.n_heads = n_heads; p.rank = rank; p.dk = dk; p.page_size = page_size; p.window = window; p.scale = scale;
     const size_t smem = sizeof(float) * ((size_t)LAT_HEADS * dk + (size_t)LAT_KEYS * (dk + 1) +
                                          LAT_HEADS * LAT_KEYS + 2 * LAT_HEADS);

@@ -1,7 +1,7 @@
 // Tensor-core attention over the one-vector-per-token latent cache (bfloat16), for prompt portions and
 // for decode tokens. Same mathematics and visibility rule as latent_attention.cu: every head of a token
 // scores its latent-space query [rank | rot] against the cached vectors [latent | rotated part] of the
-// positions it sees (j <= p and, with a window, j > p - window), softmax in float, and sums the first
+// positions it sees (j <= p and, with a window, j > p - window; a sink logit per head may join the denominator), softmax in float, and sums the first
 // `rank` elements of those vectors.
 //
 // Rows. All heads share the keys, so the rows of a sequence are the (token, head) pairs, token-major:
@@ -23,9 +23,9 @@
 
 #include "common.cuh"
 
-extern "C" int mx_attention_merge_bf16(const float* part_o, const float* part_ml, void* out, int out_stride,
-                                       int n_tokens, int n_heads, int head_dim, int n_splits,
-                                       cudaStream_t stream);
+extern "C" int mx_attention_merge_bf16_sink(const float* part_o, const float* part_ml, void* out, int out_stride,
+                                            int n_tokens, int n_heads, int head_dim, int n_splits, const float* sink,
+                                            cudaStream_t stream);
 
 namespace {
 
@@ -44,6 +44,7 @@ struct LatentMmaParams {
     const int* cu_q;
     const int* context_lens;
     const int* tiles;             // [n_tiles][2]: (sequence, first row); null: blockIdx.x is the sequence, .y the tile
+    const float* sink;            // [heads] or null: exp(sink[h]) joins a row's denominator, with no value
     int* status;
     long long n_pages;
     int bt_stride, n_heads, rank, dk, page_size, window, n_splits;
@@ -103,7 +104,7 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
     const int rows_here = min(LT_ROWS, n_rows - row0);
     const int ctx = p.context_lens[seq];
     const int hi = ctx + (row0 + rows_here - 1) / heads;
-    const int lo_tile = p.window > 0 ? max(0, ctx + row0 / heads - p.window + 1) : 0;
+    const int lo_tile = first_visible_key(ctx + row0 / heads, p.window);
     const int c_first = lo_tile / LT_KEYS, c_last = hi / LT_KEYS;
     const int per_split = (c_last - c_first + p.n_splits) / p.n_splits;
     const int c_begin = c_first + split * per_split;
@@ -150,7 +151,7 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
         const int r = row0 + rg * 16 + g + 8 * e;
         live_r[e] = r < n_rows;
         pos_r[e] = ctx + r / heads;
-        lo_r[e] = p.window > 0 ? max(0, pos_r[e] - p.window + 1) : 0;
+        lo_r[e] = first_visible_key(pos_r[e], p.window);
     }
     float o[NVT][4];
 #pragma unroll
@@ -298,7 +299,9 @@ latent_attention_mma_kernel(const LatentMmaParams p) {
         const float l = red_sum[(rg * 2) * 16 + g + 8 * r] + red_sum[(rg * 2 + 1) * 16 + g + 8 * r];
         const size_t grow = grow0 + rg * 16 + g + 8 * r;
         if (p.n_splits == 1) {
-            const float inv = 1.f / l;
+            // the sink counts once (with key splits the merge kernel adds it)
+            const float extra = p.sink ? __expf(p.sink[(int)(grow % heads)] - m_run[r]) : 0.f;
+            const float inv = 1.f / (l + extra);
             __nv_bfloat16* dst = p.out + grow * rank + col_base + 2 * tq;
 #pragma unroll
             for (int n = 0; n < NVT; ++n)
@@ -341,8 +344,8 @@ extern "C" int mx_latent_attention_mma(const void* q, const void* cache, long lo
                                        const int* block_tables, int bt_stride, const int* cu_q,
                                        const int* context_lens, const int* tiles, int n_tiles, int grid_y,
                                        int n_tokens, int n_heads, int rank, int dk, int window, float scale,
-                                       void* out, int n_splits, float* scratch, int few_rows, int* status,
-                                       cudaStream_t stream) {
+                                       void* out, int n_splits, float* scratch, int few_rows, const float* sink,
+                                       int* status, cudaStream_t stream) {
     if (n_tokens <= 0 || n_tiles <= 0) return MX_OK;
     if (!mx_latent_attention_mma_supported(rank, dk))
         MX_REFUSE("tensor-core latent attention: rank %d of a key of %d is not taken", rank, dk);
@@ -351,7 +354,7 @@ extern "C" int mx_latent_attention_mma(const void* q, const void* cache, long lo
     p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache; p.out = (__nv_bfloat16*)out;
     p.part_o = scratch;
     p.part_ml = scratch ? scratch + (size_t)n_tokens * n_heads * n_splits * rank : nullptr;
-    p.block_tables = block_tables; p.cu_q = cu_q; p.context_lens = context_lens; p.tiles = tiles;
+    p.block_tables = block_tables; p.cu_q = cu_q; p.context_lens = context_lens; p.tiles = tiles; p.sink = sink;
     p.status = status; p.n_pages = n_pages; p.bt_stride = bt_stride; p.n_heads = n_heads; p.rank = rank;
     p.dk = dk; p.page_size = page_size; p.window = window; p.n_splits = n_splits; p.scale = scale;
     // few_rows: the caller vouches that no tile has more than 16 rows (single tokens of at most 16 heads); the
@@ -365,5 +368,6 @@ extern "C" int mx_latent_attention_mma(const void* q, const void* cache, long lo
     else if (rank <= 256) rc = launch_latent_mma<16>(p, grid, smem, stream);
     else rc = launch_latent_mma<32>(p, grid, smem, stream);
     if (rc != MX_OK || n_splits == 1) return rc;
-    return mx_attention_merge_bf16(p.part_o, p.part_ml, out, n_heads * rank, n_tokens, n_heads, rank, n_splits, stream);
+    return mx_attention_merge_bf16_sink(p.part_o, p.part_ml, out, n_heads * rank, n_tokens, n_heads, rank, n_splits, sink,
+                                        stream);
 }

@@ -8,7 +8,8 @@
 //   expert's pairs (the order inside an expert is whatever the atomics make it: every row of a grouped product
 //   depends on that row alone, so the order changes no number).
 // mx_moe_route_softmax: the same outputs from another rule. The router has `n_experts + n_identity` rows; the scores
-//   are the softmax over all of them; the choice ranks score + correction[e] (a float per row, optional) and takes the
+//   are the softmax over all of them (of logit + bias[e] where a bias is given: with it and no correction the rule is
+//   "the `top` largest logits, weighted by the softmax over those alone"); the choice ranks score + correction[e] (a float per row, optional) and takes the
 //   `top` largest (ties to the lower index); the weights are the winners' plain scores over their sum (+ 1e-20). The
 //   last `n_identity` rows stand for experts without matrices that return their input: such a pair keeps its id
 //   (>= n_experts), is counted nowhere and gets no sorted row; the combine kernels add weight * input for it.
@@ -159,8 +160,9 @@ moe_route_kernel(const T* __restrict__ h, int ld, const float* __restrict__ rout
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_route_softmax_kernel(const T* __restrict__ h, int ld, const float* __restrict__ router, int K, int n_experts,
-                         int n_identity, int top, const float* __restrict__ correction, int* __restrict__ ids,
-                         float* __restrict__ weights, int* __restrict__ counts, int* __restrict__ place) {
+                         int n_identity, int top, const float* __restrict__ correction,
+                         const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
+                         int* __restrict__ counts, int* __restrict__ place) {
     extern __shared__ __align__(16) float route_s[];
     const int n_rows = n_experts + n_identity;
     float* h_s = route_s;                         // [K]
@@ -170,7 +172,10 @@ moe_route_softmax_kernel(const T* __restrict__ h, int ld, const float* __restric
     router_logits(h + (size_t)t * ld, router, K, n_rows, h_s, score);
     if (threadIdx.x >= 32) return;
     float m = -INFINITY;
-    for (int e = lane; e < n_rows; e += 32) m = fmaxf(m, score[e]);
+    for (int e = lane; e < n_rows; e += 32) {
+        if (bias) score[e] += bias[e];           // part of the logit: it moves scores, choice and weights alike
+        m = fmaxf(m, score[e]);
+    }
     m = warp_max(m);
     float sum = 0.f;
     for (int e = lane; e < n_rows; e += 32) {
@@ -469,8 +474,8 @@ extern "C" int mx_moe_route(const void* h, int dtype, int ld, const float* route
 }
 
 extern "C" int mx_moe_route_softmax(const void* h, int dtype, int ld, const float* router, int K, int n_experts,
-                                    int n_identity, int top, const float* correction, int* ids, float* weights,
-                                    int* counts, int* place, int n_tokens, cudaStream_t stream) {
+                                    int n_identity, int top, const float* correction, const float* bias, int* ids,
+                                    float* weights, int* counts, int* place, int n_tokens, cudaStream_t stream) {
     if (n_tokens <= 0) return MX_OK;
     const int n_rows = n_experts + n_identity;
     if (n_experts < 0 || n_identity < 0 || top <= 0 || top > n_rows)
@@ -479,11 +484,12 @@ extern "C" int mx_moe_route_softmax(const void* h, int dtype, int ld, const floa
     if (smem > 48 * 1024) MX_REFUSE("router: %zu bytes of shared memory for K = %d and %d rows", smem, K, n_rows);
     if (dtype == MX_DTYPE_F32)
         moe_route_softmax_kernel<float><<<n_tokens, 256, smem, stream>>>((const float*)h, ld, router, K, n_experts,
-                                                                        n_identity, top, correction, ids, weights,
-                                                                        counts, place);
+                                                                        n_identity, top, correction, bias, ids,
+                                                                        weights, counts, place);
     else
         moe_route_softmax_kernel<__nv_bfloat16><<<n_tokens, 256, smem, stream>>>(
-            (const __nv_bfloat16*)h, ld, router, K, n_experts, n_identity, top, correction, ids, weights, counts, place);
+            (const __nv_bfloat16*)h, ld, router, K, n_experts, n_identity, top, correction, bias, ids, weights, counts,
+            place);
     return mx_launch_status();
 }
 

@@ -1,7 +1,10 @@
 // RMS norm over rows of the float residual stream, and the post-norm step that forms its own input.
 //
 //   unit(x) = x / sqrt(mean(x^2) + eps)          (eps inside the root)
-//   mx_rmsnorm:      out[r] = unit(x[rows ? rows[r] : r]) * (offset + weight)
+//   mx_rmsnorm:      out[r] = unit(x[rows ? rows[r] : r]) * (offset + weight)      (rows of x `x_stride` floats apart)
+//   mx_rmsnorm_branch_add: x[r] <- x[r] + unit(y[r]) * wb      (in place, float: a branch normalised on its way in)
+//                    out[r] <- unit(x[r]) * wn in the activation dtype (the next sublayer's normalised input;
+//                    wn null: x[r] itself, rounded; out null: nothing)
 //   mx_rmsnorm_sum:  x[r]  <- unit(alpha * x[r] + acc[r]) * (offset + weight)   (in place, float)
 //                    act[r] <- the same row rounded to the activation dtype (optional)
 //
@@ -23,10 +26,10 @@ constexpr int RMS_MAX_PER_THREAD = 16;   // row values a thread keeps in registe
 template <typename TOut>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                const float* __restrict__ weight, float offset, TOut* __restrict__ out,
-                               int hidden, float eps) {
+                               int hidden, float eps, long long x_stride) {
     __shared__ float scratch[32];
     const int r = blockIdx.x;
-    const float* xr = x + (size_t)(rows ? rows[r] : r) * hidden;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * x_stride;
     float s = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         const float v = xr[i];
@@ -110,6 +113,51 @@ __global__ void rmsnorm_sum_vec_kernel(float* x, const float* __restrict__ acc, 
     }
 }
 
+// x += unit(y) * wb, then out = unit(x) * wn (or x, or nothing): one block per row, both rows in registers
+// (longer rows are read again), float statistics in an order that the thread layout alone fixes.
+template <typename TAct>
+__global__ void rmsnorm_branch_add_kernel(float* x, const float* y, const float* __restrict__ wb,
+                                          const float* __restrict__ wn, TAct* out, int hidden, float eps) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    x = after_wait(x);
+    y = after_wait(y);
+    const int r = blockIdx.x;
+    float* xr = x + (size_t)r * hidden;
+    const float* yr = y + (size_t)r * hidden;
+    float kept[RMS_MAX_PER_THREAD];
+    float s = 0.f;
+    int n = 0;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x, ++n) {
+        const float v = yr[i];
+        if (n < RMS_MAX_PER_THREAD) kept[n] = v;
+        s = fmaf(v, v, s);
+    }
+    const float inv_y = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + eps);
+    s = 0.f;
+    n = 0;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x, ++n) {
+        const float b = n < RMS_MAX_PER_THREAD ? kept[n] : yr[i];
+        const float v = xr[i] + b * inv_y * wb[i];
+        xr[i] = v;
+        if (n < RMS_MAX_PER_THREAD) kept[n] = v;
+        s = fmaf(v, v, s);
+    }
+    if (out == nullptr) return;
+    TAct* o = out + (size_t)r * hidden;
+    if (wn == nullptr) {
+        n = 0;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x, ++n)
+            o[i] = from_float<TAct>(n < RMS_MAX_PER_THREAD ? kept[n] : xr[i]);
+        return;
+    }
+    const float inv_x = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + eps);
+    n = 0;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x, ++n)
+        o[i] = from_float<TAct>((n < RMS_MAX_PER_THREAD ? kept[n] : xr[i]) * inv_x * wn[i]);
+}
+
 __global__ void cast_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long long count) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < count) out[i] = __float2bfloat16_rn(x[i]);
@@ -120,15 +168,30 @@ int threads_for(int hidden) { return hidden >= 4096 ? 512 : (hidden >= 1024 ? 25
 }  // namespace
 
 extern "C" int mx_rmsnorm(const float* x, const int* rows, const float* weight, float offset, void* out,
-                          int out_dtype, int n_rows, int hidden, float eps, cudaStream_t stream) {
+                          int out_dtype, int n_rows, int hidden, float eps, long long x_stride, cudaStream_t stream) {
     if (n_rows <= 0) return MX_OK;
     if (hidden <= 0) MX_REFUSE("rmsnorm: hidden must be positive, got %d", hidden);
     const int threads = threads_for(hidden);
     if (out_dtype == MX_DTYPE_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, rows, weight, offset, (float*)out, hidden, eps);
+        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, rows, weight, offset, (float*)out, hidden, eps, x_stride);
     else
         rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, rows, weight, offset,
-                                                                     (__nv_bfloat16*)out, hidden, eps);
+                                                                     (__nv_bfloat16*)out, hidden, eps, x_stride);
+    return mx_launch_status();
+}
+
+extern "C" int mx_rmsnorm_branch_add(float* x, const float* y, const float* wb, const float* wn, void* out,
+                                     int out_dtype, int n_rows, int hidden, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return MX_OK;
+    if (hidden <= 0) MX_REFUSE("rmsnorm: hidden must be positive, got %d", hidden);
+    // few rows (a decode step): the row's latency is all there is, so more threads a row
+    const int threads = n_rows <= 64 ? min(1024, max(128, (hidden + 127) / 128 * 32)) : threads_for(hidden);
+    if (out_dtype == MX_DTYPE_F32)
+        mx_launch_chained(rmsnorm_branch_add_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, y, wb, wn,
+                          (float*)out, hidden, eps);
+    else
+        mx_launch_chained(rmsnorm_branch_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, y, wb,
+                          wn, (__nv_bfloat16*)out, hidden, eps);
     return mx_launch_status();
 }
 

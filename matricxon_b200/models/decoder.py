@@ -64,6 +64,8 @@ def model_weight_specs(spec: ModelSpec) -> list[WeightSpec]:
     for index, layer in enumerate(spec.layers):
         specs.extend(part_class("block", layer.block).weight_specs(layer, spec.layer_prefix_of(index)))
     specs.extend(part_class("norm", spec.final_norm.kind).weight_specs(spec.final_norm, spec.norm_prefix))
+    if spec.pass_input is not None:
+        specs.extend(part_class("pass_input", spec.pass_input.kind).weight_specs(spec.pass_input, ""))
     if not spec.tie_word_embeddings:
         specs.append(WeightSpec(f"{spec.head_name}{spec.weight_suffix}", (spec.vocab_size, spec.hidden_size),
                                 role="matrix", init="weight"))
@@ -128,8 +130,12 @@ class DecoderModel:
         self.layers = [part_class("block", layer.block)(layer, runtime, spec.layer_prefix_of(index))
                        for index, layer in enumerate(spec.layers)]
         self.final_norm = build_part("norm", spec.final_norm, runtime, spec.norm_prefix)
+        # what runs before the entries that open a pass of a repeated run (its tensors carry full names)
+        self.pass_input = (build_part("pass_input", spec.pass_input, runtime, "")
+                           if spec.pass_input is not None else None)
         # decode steps may be captured as CUDA graphs only if every part is stream-ordered
-        self.capturable = self.final_norm.capturable and all(layer.capturable for layer in self.layers)
+        self.capturable = (self.final_norm.capturable and all(layer.capturable for layer in self.layers)
+                           and (self.pass_input is None or self.pass_input.capturable))
         self.cache_plan = plan_cache(spec)
         self.embedding: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
@@ -160,6 +166,8 @@ class DecoderModel:
         for layer in self.layers:
             layer.load(fetch)
         self.final_norm.load(fetch)
+        if self.pass_input is not None:
+            self.pass_input.load(fetch)
         self.head = (self.embedding if self.spec.tie_word_embeddings
                      else fetch(f"{self.spec.head_name}{self.spec.weight_suffix}"))
         self.head_bias = fetch(f"{self.spec.head_name}.bias") if self.spec.head_bias else None
@@ -184,11 +192,24 @@ class DecoderModel:
         # a block may hand the next one a residual sum still to be added up (the next norm adds as it reads)
         ctx.pending_sum_wanted = True
         taps = ctx.memo.get("layer_outputs")
+        if self.pass_input is not None:
+            self.pass_input.begin(x, ctx)
+        schedule = self.spec.schedule
         try:
-            for position, entry in enumerate(self.spec.schedule):
+            for position, entry in enumerate(schedule):
                 layer = self.layers[entry.layer]
+                if entry.pass_index is not None:
+                    if isinstance(x, PendingSum):
+                        x = x.tensor()
+                    x = self.pass_input.forward(x, entry.pass_index, ctx)
                 if isinstance(x, PendingSum) and not layer.takes_pending_sum:
                     x = x.tensor()
+                # a block that ends in a norm kernel of its own may apply the next block's first norm on its way out
+                # (not across a pass input, which changes the stream in between)
+                follower = None
+                if position + 1 < len(schedule) and schedule[position + 1].pass_index is None:
+                    follower = getattr(self.layers[schedule[position + 1].layer], "input_norm", None)
+                ctx.next_input_norm = follower
                 x = layer.forward(x, ctx, self.bindings[position])
                 if taps is not None:        # a caller that wants the stream after every schedule entry
                     if isinstance(x, PendingSum):
@@ -196,6 +217,7 @@ class DecoderModel:
                     taps.append(x.clone())
         finally:
             ctx.pending_sum_wanted = False
+            ctx.next_input_norm = None
         return x.tensor() if isinstance(x, PendingSum) else x      # the last block's sum, added up here
 
     def logits(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

@@ -524,17 +524,19 @@ def mma_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int, q
 # ---------------------------------------------------------------------- RMS norm, post-norm sums
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, offset: float, eps: float, out: torch.Tensor,
             rows: torch.Tensor | None = None) -> None:
-    """out[r] = x[row] / sqrt(mean(x[row]^2) + eps) * (offset + weight), row = rows[r] if given else r."""
-    _need(x, "x", torch.float32)
+    """out[r] = x[row] / sqrt(mean(x[row]^2) + eps) * (offset + weight), row = rows[r] if given else r. ``x`` may be
+    the first columns of wider rows (a view with a row stride)."""
+    _need(x, "x", torch.float32, contiguous=False)
+    assert x.stride(1) == 1
     _need(weight, "weight", torch.float32)
     _need(out, "out")
     if rows is not None:
         _need(rows, "rows", torch.int32)
     n_rows, hidden = out.shape
-    assert x.shape[1] == hidden and weight.numel() == hidden
+    assert x.shape[1] >= hidden and weight.numel() == hidden
     assert (rows.numel() if rows is not None else x.shape[0]) == n_rows
     check(library().mx_rmsnorm(_ptr(x), _ptr(rows), _ptr(weight), float(offset), _ptr(out),
-                               dtype_code(out.dtype), n_rows, hidden, float(eps), _stream()), "rmsnorm")
+                               dtype_code(out.dtype), n_rows, hidden, float(eps), x.stride(0), _stream()), "rmsnorm")
     _launched()
 
 
@@ -552,6 +554,28 @@ def rmsnorm_sum(x: torch.Tensor, acc: torch.Tensor, alpha: float, weight: torch.
     check(library().mx_rmsnorm_sum(_ptr(x), _ptr(acc), float(alpha), _ptr(weight), float(offset), _ptr(act),
                                    dtype_code(act.dtype) if act is not None else F32, x.shape[0], x.shape[1],
                                    float(eps), _stream()), "rmsnorm_sum")
+    _launched()
+
+
+def rmsnorm_branch_add(x: torch.Tensor, branch: torch.Tensor, branch_weight: torch.Tensor,
+                       next_weight: torch.Tensor | None, out: torch.Tensor | None, eps: float) -> None:
+    """``x <- x + unit(branch) * branch_weight`` in place (float32, ``unit(v) = v / sqrt(mean(v^2) + eps)``); then
+    ``out`` (any activation dtype, or None) gets ``unit(x) * next_weight``, or the new ``x`` itself when
+    ``next_weight`` is None."""
+    _need(x, "x", torch.float32)
+    _need(branch, "branch", torch.float32)
+    _need(branch_weight, "branch_weight", torch.float32)
+    n, hidden = x.shape
+    assert tuple(branch.shape) == (n, hidden) and branch_weight.numel() == hidden
+    if next_weight is not None:
+        _need(next_weight, "next_weight", torch.float32)
+        assert next_weight.numel() == hidden and out is not None
+    if out is not None:
+        _need(out, "out")
+        assert tuple(out.shape) == (n, hidden)
+    check(library().mx_rmsnorm_branch_add(_ptr(x), _ptr(branch), _ptr(branch_weight), _ptr(next_weight), _ptr(out),
+                                          dtype_code(out.dtype) if out is not None else F32, n, hidden, float(eps),
+                                          _stream()), "rmsnorm_branch_add")
     _launched()
 
 
@@ -617,12 +641,19 @@ def gemm_batched_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> 
 def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, amplitude: float,
                    latent_weight: torch.Tensor, eps: float, slots: torch.Tensor | None,
                    cache: torch.Tensor | None, q_plain: torch.Tensor, q_lat: torch.Tensor, n_heads: int,
-                   dim: int, rot: int, rot_dims: int, rank: int, status: torch.Tensor) -> None:
+                   dim: int, rot: int, rot_dims: int, rank: int, status: torch.Tensor,
+                   down: torch.Tensor | None = None, interleaved: bool = False) -> None:
     """From the float rows ``[heads x (dim | rot) | rank | rot]`` of the fused query / down projection:
     the plain query parts, the rotated query parts (at offset ``rank`` of each head of ``q_lat``) and the
     token's cache vector ``[unit(latent) * latent_weight | rotated shared part]`` at ``slots``.
-    ``cache`` is [pages, 1, 1, page_size, rank + rot]; None stores nothing."""
-    _need(proj, "proj", torch.float32)
+    ``cache`` is [pages, 1, 1, page_size, rank + rot]; None stores nothing. ``down`` (float rows ``[rank | rot]``,
+    rows may be strided): the latent and the shared part come from there and ``proj`` holds the query heads only.
+    ``interleaved`` pairs entry 2i with 2i + 1 in the rotation instead of i with i + rot_dims/2."""
+    _need(proj, "proj", torch.float32, contiguous=False)
+    if down is not None:
+        _need(down, "down", torch.float32, contiguous=False)
+        assert down.stride(1) == 1 and down.shape[0] >= proj.shape[0] and down.shape[1] >= rank + rot
+    assert proj.stride(1) == 1
     _need(positions, "positions", torch.int32)
     _need(freq, "freq", torch.float32)
     _need(latent_weight, "latent_weight", torch.float32)
@@ -637,7 +668,8 @@ def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, freq: torch.Tens
         _need(slots, "slots", torch.int32)
         assert tuple(cache.shape[1:3]) == (1, 1) and cache.shape[4] == rank + rot, cache.shape
         n_pages, page_size = cache.shape[0], cache.shape[3]
-    check(library().mx_latent_prepare(_ptr(proj), proj.stride(0), _ptr(positions), _ptr(freq), float(amplitude),
+    check(library().mx_latent_prepare(_ptr(proj), proj.stride(0), _ptr(down), down.stride(0) if down is not None else 0,
+                                      1 if interleaved else 0, _ptr(positions), _ptr(freq), float(amplitude),
                                       _ptr(latent_weight), float(eps), _ptr(slots), _ptr(cache), n_pages,
                                       page_size, _ptr(q_plain), _ptr(q_lat), dtype_code(q_plain.dtype), n,
                                       n_heads, dim, rot, rot_dims, rank, _ptr(status), _stream()),
@@ -647,10 +679,10 @@ def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, freq: torch.Tens
 
 def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
                      tok_seq: torch.Tensor, positions: torch.Tensor, rank: int, window: int | None,
-                     scale: float, out: torch.Tensor, status: torch.Tensor) -> None:
+                     scale: float, out: torch.Tensor, status: torch.Tensor, sink: torch.Tensor | None = None) -> None:
     """Attention of ``q_lat`` [tokens, heads, dk] over the one-vector-per-token cache
     [pages, 1, 1, page_size, dk]; ``out`` [tokens, heads, rank] is the softmax-weighted sum of the first
-    ``rank`` elements of the visible vectors."""
+    ``rank`` elements of the visible vectors. ``sink`` (float32, one logit per head) joins the denominator."""
     _need(q_lat, "q_lat")
     _need(cache, "cache", q_lat.dtype)
     _need(out, "out", q_lat.dtype)
@@ -663,7 +695,8 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, block_tables: tor
     check(library().mx_latent_attention(_ptr(q_lat), _ptr(cache), dtype_code(q_lat.dtype), cache.shape[0],
                                         cache.shape[3], _ptr(block_tables), block_tables.stride(0),
                                         _ptr(tok_seq), _ptr(positions), n, n_heads, rank, dk, int(window or 0),
-                                        float(scale), _ptr(out), _ptr(status), _stream()), "latent_attention")
+                                        float(scale), _ptr(out), _sink_ptr(sink, n_heads), _ptr(status), _stream()),
+          "latent_attention")
     _launched()
 
 
@@ -688,7 +721,7 @@ def latent_attention_mma(q_lat: torch.Tensor, cache: torch.Tensor, block_tables:
                          cu_q: torch.Tensor, context_lens: torch.Tensor, tiles: torch.Tensor | None,
                          n_tiles: int, rank: int, window: int | None, scale: float, out: torch.Tensor,
                          status: torch.Tensor, n_splits: int = 1, scratch: torch.Tensor | None = None,
-                         few_rows: bool = False) -> None:
+                         few_rows: bool = False, sink: torch.Tensor | None = None) -> None:
     """``latent_attention`` on the tensor cores (bfloat16). ``few_rows``: the caller vouches that every
     sequence brings at most 16 (token, head) rows, which lets the kernel keep more keys in flight. ``tiles`` is int32 [n_tiles, 2] from
     ``latent_tile_list``; None means that tile i is sequence i (a fixed-size batch of decoding requests,
@@ -717,7 +750,7 @@ def latent_attention_mma(q_lat: torch.Tensor, cache: torch.Tensor, block_tables:
         _ptr(q_lat), _ptr(cache), cache.shape[0], cache.shape[3], _ptr(block_tables), block_tables.stride(0),
         _ptr(cu_q), _ptr(context_lens), _ptr(tiles), n_tiles, (n_heads + 63) // 64, n, n_heads, rank, dk,
         int(window or 0), float(scale), _ptr(out), int(n_splits), _ptr(scratch) if n_splits > 1 else None,
-        1 if few_rows else 0, _ptr(status), _stream()), "latent_attention_mma")
+        1 if few_rows else 0, _sink_ptr(sink, n_heads), _ptr(status), _stream()), "latent_attention_mma")
     _launched(2 if n_splits > 1 else 1)
 
 
@@ -1121,8 +1154,11 @@ def moe_combine(pairs: torch.Tensor, residual: torch.Tensor, top: int, identity=
 
 
 def moe_route_softmax(h: torch.Tensor, router: torch.Tensor, top: int, n_identity: int, correction: torch.Tensor | None,
-                      ids: torch.Tensor, weights: torch.Tensor, counts: torch.Tensor, place: torch.Tensor) -> None:
-    """Per token: softmax scores over the rows of the float32 router [experts + n_identity, K]; the ``top`` rows
+                      ids: torch.Tensor, weights: torch.Tensor, counts: torch.Tensor, place: torch.Tensor,
+                      bias: torch.Tensor | None = None) -> None:
+    """Per token: softmax scores over the rows of the float32 router [experts + n_identity, K] (``bias``, float32 per
+    row or None, is added to the logits first: with a bias and no correction the rule reads "the ``top`` largest
+    logits, weighted by the softmax over those alone"); the ``top`` rows
     with the largest ``score + correction`` (float32 per row or None; ties to the lower index); weights = the
     chosen rows' plain scores / their sum. ``counts`` [experts] must be zero; afterwards it holds every expert's
     pairs and ``place`` each pair's index among them. A pair of one of the last ``n_identity`` rows keeps its id,
@@ -1139,8 +1175,11 @@ def moe_route_softmax(h: torch.Tensor, router: torch.Tensor, top: int, n_identit
     if correction is not None:
         _need(correction, "correction", torch.float32)
         assert correction.numel() == router.shape[0]
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == router.shape[0]
     check(library().mx_moe_route_softmax(_ptr(h), dtype_code(h.dtype), h.stride(0), _ptr(router), k, n_experts, n_identity,
-                                         top, _ptr(correction), _ptr(ids), _ptr(weights), _ptr(counts), _ptr(place), n,
+                                         top, _ptr(correction), _ptr(bias), _ptr(ids), _ptr(weights), _ptr(counts), _ptr(place), n,
                                          _stream()), "moe_route_softmax")
     _launched()
 
@@ -1312,4 +1351,41 @@ def rotate_norm_kv_write(proj: torch.Tensor, positions: torch.Tensor, freq: torc
                                             _ptr(cache), n_pages, page_size, _ptr(q_out), dtype_code(q_out.dtype), n,
                                             n_heads, n_kv_heads, dim, vdim, hd, _ptr(status), _stream()),
           "rotate_norm_kv_write")
+    _launched()
+
+
+def norm_rotate_kv_write(proj: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, rot: int, interleaved: bool,
+                         q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
+                         slots: torch.Tensor | None, cache: torch.Tensor | None, q_out: torch.Tensor, n_heads: int,
+                         n_kv_heads: int, dim: int, vdim: int, status: torch.Tensor) -> None:
+    """From float rows ``[q | k | v | ...]`` of a fused projection: q and k heads RMS-normalised over ``dim`` with the
+    weights ``q_weight`` / ``k_weight`` (float32 [dim]; None: left as they are; ``eps`` inside the root) and then
+    rotated over their first ``rot`` entries (pairs (i, i + rot/2) or, ``interleaved``, (2i, 2i + 1); angle
+    ``position * freq[i]``); q into ``q_out`` [tokens, heads * hd], k and v into the paged ``cache``
+    [pages, 2, kv heads, page_size, hd] at ``slots`` (both None: nothing is stored). ``hd`` is the padded head size of
+    ``q_out``; tails are zero."""
+    _need(proj, "proj", torch.float32, contiguous=False)
+    _need(positions, "positions", torch.int32)
+    _need(freq, "freq", torch.float32)
+    _need(q_out, "q_out")
+    _need(status, "status", torch.int32)
+    n = q_out.shape[0]
+    hd = q_out.shape[1] // n_heads
+    assert q_out.shape[1] == n_heads * hd and proj.stride(1) == 1 and proj.shape[0] >= n
+    assert freq.numel() >= rot // 2
+    for name, weight in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if weight is not None:
+            _need(weight, name, torch.float32)
+            assert weight.numel() == dim
+    n_pages, page_size = 0, 1
+    if cache is not None:
+        _need(cache, "cache", q_out.dtype)
+        _need(slots, "slots", torch.int32)
+        n_pages, page_size = cache.shape[0], cache.shape[3]
+        assert tuple(cache.shape[1:]) == (2, n_kv_heads, page_size, hd), cache.shape
+    check(library().mx_norm_rotate_kv_write(_ptr(proj), proj.stride(0), _ptr(positions), _ptr(freq), int(rot),
+                                            1 if interleaved else 0, _ptr(q_weight), _ptr(k_weight), float(eps),
+                                            _ptr(slots) if cache is not None else None, _ptr(cache), n_pages, page_size,
+                                            _ptr(q_out), dtype_code(q_out.dtype), n, n_heads, n_kv_heads, dim, vdim, hd,
+                                            _ptr(status), _stream()), "norm_rotate_kv_write")
     _launched()

@@ -45,13 +45,14 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_paged_attention_tc": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, F, P, I, P, P], I),
     "mx_paged_attention_tc_split": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, F, P, I, I, P, P, F, P, I, P], I),
     "mx_paged_attention": ([P, I, I, P, L, I, P, I, P, P, I, I, I, I, I, F, P, I, I, P, P, F, P, I, P], I),
-    "mx_rmsnorm": ([P, P, P, F, P, I, I, I, F, P], I),
+    "mx_rmsnorm": ([P, P, P, F, P, I, I, I, F, L, P], I),
+    "mx_rmsnorm_branch_add": ([P, P, P, P, P, I, I, I, F, P], I),
     "mx_rmsnorm_sum": ([P, P, F, P, F, P, I, I, I, F, P], I),
     "mx_cast_rows": ([P, P, L, P], I),
-    "mx_latent_prepare": ([P, I, P, P, F, P, F, P, P, L, I, P, P, I, I, I, I, I, I, I, P, P], I),
+    "mx_latent_prepare": ([P, I, P, I, I, P, P, F, P, F, P, P, L, I, P, P, I, I, I, I, I, I, I, P, P], I),
     "mx_latent_attention_mma_supported": ([I, I], I),
-    "mx_latent_attention_mma": ([P, P, L, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, I, P, I, P, P], I),
-    "mx_latent_attention": ([P, P, I, L, I, P, I, P, P, I, I, I, I, I, F, P, P, P], I),
+    "mx_latent_attention_mma": ([P, P, L, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, I, P, I, P, P, P], I),
+    "mx_latent_attention": ([P, P, I, L, I, P, I, P, P, I, I, I, I, I, F, P, P, P, P], I),
     "mx_qk_norm_kv_write": ([P, I, P, P, F, P, P, L, I, P, I, I, I, I, I, I, I, P, P], I),
     "mx_sigmoid_gate": ([P, P, I, P, I, I, I, I, I, P], I),
     "mx_clamped_glu": ([P, I, P, I, I, I, F, F, F, P], I),
@@ -65,7 +66,7 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_gla_scan": ([P, I, I, I, I, P, F, P, P, P, P, I, I, I, I, P], I),
     "mx_gla_norm_gate": ([P, P, I, P, F, P, I, I, I, I, P], I),
     "mx_moe_route": ([P, I, I, P, I, I, I, I, I, F, P, P, P, P, I, P], I),
-    "mx_moe_route_softmax": ([P, I, I, P, I, I, I, I, P, P, P, P, P, I, P], I),
+    "mx_moe_route_softmax": ([P, I, I, P, I, I, I, I, P, P, P, P, P, P, I, P], I),
     "mx_moe_tile_rows": ([], I),
     "mx_moe_plan": ([P, P, P, I, I, I, P, P, P, P, P], I),
     "mx_moe_gather": ([P, I, P, I, P, I, I, P], I),
@@ -74,6 +75,7 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_moe_gemm": ([P, I, I, P, I, P, L, I, I, P, P, I, P, P, I, I, F, F, F, P], I),
     "mx_moe_combine": ([P, P, I, I, I, P, P, P, I, I, I, P], I),
     "mx_rotate_norm_kv_write": ([P, I, P, P, I, F, P, P, L, I, P, I, I, I, I, I, I, I, P, P], I),
+    "mx_norm_rotate_kv_write": ([P, I, P, P, I, I, P, P, F, P, P, L, I, P, I, I, I, I, I, I, I, P, P], I),
     "mx_layernorm_scaled_add": ([P, P, P, P, P, P, I, I, I, F, I, P], I),
     "mx_gelu_gate_rows": ([P, I, P, P, I, I, I, P, I, I, I, P, P], I),
     "mx_scale_rows": ([P, L, F, P], I),

@@ -1,7 +1,7 @@
 """Parts a model is assembled from. Importing this package registers the built-in kinds."""
 
 from matricxon_b200.parts import (  # noqa: F401  (registration)
-    attention, block, latent_attention, linear_attention, mlp, norm, recurrent, rotary, routed, side_input)
+    attention, block, latent_attention, linear_attention, mlp, norm, pass_input, recurrent, rotary, routed, side_input)
 from matricxon_b200.parts.base import (
     Block,
     CacheBinding,

@@ -54,6 +54,21 @@ def _key_span(ctx, window: int | None) -> int:
     return ctx.max_kv_len if window is None else min(ctx.max_kv_len, window)
 
 
+class _SpanLimited:
+    """A step context whose longest key range is capped (a mask that never shows a query more than ``limit`` keys):
+    what sizes the key splits. Everything else is the context's own."""
+
+    def __init__(self, ctx, limit: int) -> None:
+        self._ctx, self._limit = ctx, limit
+
+    @property
+    def max_kv_len(self) -> int:
+        return min(self._ctx.max_kv_len, self._limit)
+
+    def __getattr__(self, name):
+        return getattr(self._ctx, name)
+
+
 def mma_tile_splits(ctx, n_tiles: int, narrow: bool, alone: bool, n_heads: int, n_kv_heads: int,
                     head_dim: int, window: int | None):
     """Key splits for one launch of the mma.sync attention (a block per tile, KV head and
@@ -100,19 +115,30 @@ def simt_splits(ctx, n_heads: int, n_kv_heads: int, head_dim: int, window: int |
 
 
 def paged_attend(q, q_stride, ctx, binding, rt, n_heads, n_kv_heads, head_dim, window, scale, softcap=None,
-                 sink=None, keep_first=0):
+                 sink=None, keep_first=0, chunk=None):
     """Attention of the step's query rows (``q``: query head h of a row at column ``h * head_dim``, rows
     ``q_stride`` apart) over the keys and values already stored in ``binding.kv``: picks the kernel, the
     tiles and the key splits for this step. Returns [tokens, heads * head_dim] in the runtime dtype.
     ``softcap`` caps the scaled scores at ``softcap * tanh(score / softcap)``; ``sink`` (float32, one logit per
     head) joins the softmax's denominator without a value. ``keep_first``: under a window, the keys of the
-    sequence's first ``keep_first`` positions stay visible at any distance. Every kernel takes cap, sink and kept
-    tokens."""
-    keep_first = int(keep_first) if window is not None else 0
+    sequence's first ``keep_first`` positions stay visible at any distance. ``chunk`` (instead of a window): the
+    sequence is cut into blocks of ``chunk`` positions counted from its start and a query sees the keys of its own
+    block only; the kernels take this rule as a negative ``window``. Every kernel takes cap, sink, kept tokens and
+    blocks."""
+    if chunk is not None:
+        if window is not None:
+            raise ValueError("attention is masked by a window or by blocks, not both")
+        if int(chunk) <= 0:
+            raise ValueError(f"blocks hold at least one position, got {chunk}")
+        # a query walks at most the keys of one block
+        attn = paged_attend(q, q_stride, _SpanLimited(ctx, int(chunk)), binding, rt, n_heads, n_kv_heads, head_dim,
+                            -int(chunk), scale, softcap=softcap, sink=sink)
+        return attn
+    keep_first = int(keep_first) if window is not None and window > 0 else 0
     extras = {"softcap": softcap, "sink": sink}
     kept = {"keep_first": keep_first}
     # the kept keys are walked beside the window's: the span that sizes the key splits grows by them
-    span = None if window is None else window + keep_first
+    span = None if window is None or window < 0 else window + keep_first
     group = ctx.groups[binding.group]
     attn = torch.empty((ctx.n_tokens, n_heads * head_dim), dtype=rt.dtype, device=q.device)
     if kernels.mma_attention_supported(rt.dtype, head_dim, rt.page_size, q_stride):
@@ -484,6 +510,113 @@ class UnitNormAttention(Mixer):
         attn = paged_attend(q, q.stride(0), ctx, binding, rt, s.num_heads, s.num_kv_heads, hd, s.window, s.scale,
                             keep_first=s.keep_first)
         if hd != s.value_dim:
+            attn = attn.view(n, s.num_heads, hd)[:, :, :s.value_dim].reshape(n, -1)
+        if residual is None:
+            return linear(attn, self.o_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
+        return linear(attn, self.o_weight, None, EPILOGUE_RESIDUAL, residual=residual, out=residual,
+                      backend=rt.gemm_backend, defer_sum=getattr(ctx, "sums_may_pend", False))
+
+
+@register_part("mixer", "normed_rotary_attention")
+class NormedRotaryAttention(Mixer):
+    """Grouped-query attention without biases whose queries and keys are RMS-normalised head by head with a learned
+    weight and then rotated over their first entries; causal, windowed or cut into blocks; with an ordinary softmax,
+    one added to its denominator, or a learned sink; optionally capped scores; a sigmoid gate per head or per entry
+    that reads the mixer's input (``NormedRotaryAttentionSpec``).
+
+    One fused product gives float rows ``[q | k | v | gate]``; one kernel normalises and rotates q and k in float and
+    stores k and v in the paged cache in the layout the stock attention kernels read (``paged_attend``, which knows
+    every mask, the cap and the sink), every head padded with zeros to a common size of a multiple of 16 when the key
+    and value widths differ or are no such multiple; one kernel applies the gate and drops the padding.
+    ``forward(h, None, ...)`` returns the mixer's float output without a residual."""
+
+    capturable = True
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        self.padded_dim = self.cache_head_dim(spec)
+        self.position = (build_part("position", spec.position, runtime, prefix)
+                         if spec.position is not None and spec.position.rotary_dim > 0 else None)
+        if self.position is not None and not hasattr(self.position, "frequencies"):
+            raise ValueError(f"position encoding {spec.position.kind!r} offers no frequency table")
+        self.gate_rows = {None: 0, "head": spec.num_heads, "entry": spec.num_heads * spec.value_dim}[spec.gate]
+
+    @staticmethod
+    def cache_head_dim(spec) -> int:
+        return -(-max(spec.head_dim, spec.value_dim) // 16) * 16
+
+    @classmethod
+    def _matrices(cls, spec):
+        shapes = [(spec.query_name, (spec.num_heads * spec.head_dim, spec.hidden_size)),
+                  (spec.key_name, (spec.num_kv_heads * spec.head_dim, spec.hidden_size)),
+                  (spec.value_name, (spec.num_kv_heads * spec.value_dim, spec.hidden_size))]
+        if spec.gate == "head":
+            shapes.append((spec.gate_name, (spec.num_heads, spec.hidden_size)))
+        elif spec.gate == "entry":
+            shapes.append((spec.gate_name, (spec.num_heads * spec.value_dim, spec.hidden_size)))
+        return shapes
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        specs = [WeightSpec(prefix + name, shape, role="matrix", init="weight") for name, shape in cls._matrices(spec)]
+        specs.append(WeightSpec(prefix + spec.output_name, (spec.hidden_size, spec.num_heads * spec.value_dim),
+                                role="matrix", init="weight"))
+        for name in (spec.query_norm_name, spec.key_norm_name):
+            if name is not None:
+                specs.append(WeightSpec(prefix + name, (spec.head_dim,), role="vector", init="norm_weight"))
+        if spec.sink == "learned":
+            specs.append(WeightSpec(prefix + spec.sink_name, (spec.num_heads,), role="vector", init="bias"))
+        return specs
+
+    @classmethod
+    def cache_request(cls, spec):
+        # blocks are kept whole (a later query of the same block needs them); only a window gives pages back
+        return KVCacheRequest(num_kv_heads=spec.num_kv_heads, head_dim=cls.cache_head_dim(spec),
+                              window=spec.mask_size if spec.mask == "window" else None)
+
+    def load(self, fetch):
+        p, s = self.prefix, self.spec
+        self.proj_weight = torch.cat([fetch(p + name) for name, _ in self._matrices(s)])
+        self.o_weight = fetch(p + s.output_name)
+        self.q_norm = fetch(p + s.query_norm_name) if s.query_norm_name is not None else None
+        self.k_norm = fetch(p + s.key_norm_name) if s.key_norm_name is not None else None
+        if s.sink == "learned":
+            self.sink = fetch(p + s.sink_name)
+        elif s.sink == "zero":
+            self.sink = torch.zeros(s.num_heads, dtype=torch.float32, device=self.runtime.device)
+        else:
+            self.sink = None
+
+    def forward(self, h, residual, ctx, binding):
+        s, rt, hd = self.spec, self.runtime, self.padded_dim
+        if binding.kv is None:
+            raise RuntimeError("attention needs cache pages bound to it")
+        n = h.shape[0]
+        proj = linear(h, self.proj_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
+        q = torch.empty((n, s.num_heads * hd), dtype=rt.dtype, device=h.device)
+        writes = binding.writes
+        if self.position is not None:
+            freq, rot = self.position.frequencies, s.position.rotary_dim
+            interleaved = bool(getattr(self.position, "interleaved", False))
+        else:
+            freq, rot, interleaved = torch.empty(0, dtype=torch.float32, device=h.device), 0, False
+        kernels.norm_rotate_kv_write(proj, ctx.positions, freq, rot, interleaved, self.q_norm, self.k_norm, s.eps,
+                                     ctx.groups[binding.group].slots if writes else None,
+                                     binding.kv if writes else None, q, s.num_heads, s.num_kv_heads, s.head_dim,
+                                     s.value_dim, ctx.status)
+        attn = paged_attend(q, q.stride(0), ctx, binding, rt, s.num_heads, s.num_kv_heads, hd,
+                            s.mask_size if s.mask == "window" else None, s.scale, softcap=s.softcap, sink=self.sink,
+                            chunk=s.mask_size if s.mask == "chunk" else None)
+        if s.gate is not None:
+            gate_col = (s.num_heads + s.num_kv_heads) * s.head_dim + s.num_kv_heads * s.value_dim
+            gated = torch.empty((n, s.num_heads * s.value_dim), dtype=rt.dtype, device=h.device)
+            gate = proj[:, gate_col:gate_col + self.gate_rows]
+            if s.gate == "head":
+                kernels.head_gate(attn, gate, gated, s.num_heads, s.value_dim)
+            else:
+                kernels.sigmoid_gate(attn, gate, gated, s.num_heads, s.value_dim)
+            attn = gated
+        elif hd != s.value_dim:
             attn = attn.view(n, s.num_heads, hd)[:, :, :s.value_dim].reshape(n, -1)
         if residual is None:
             return linear(attn, self.o_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)

@@ -17,6 +17,7 @@ Interfaces (duck-typed; these base classes state them):
   Mixer.cache_request(spec) / Mixer.state_request(spec): what the cache manager must hold.
   FeedForward.forward(h, residual, ctx) -> residual + ffn(h)          (float32)
   SideInput.forward(x, h, ctx) -> (x, activations)                     (x updated in place; h = x in the runtime dtype)
+  PassInput.begin(x0, ctx); PassInput.forward(x, pass_index, ctx) -> x  (before the entry that opens a pass)
   Block.forward(x, ctx, binding) -> x                                  (float32)
 """
 
@@ -29,7 +30,7 @@ import torch
 
 from matricxon_b200.weights.loader import WeightSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "side_input", "block")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "side_input", "pass_input", "block")
 _PARTS: dict[str, dict[str, type]] = {category: {} for category in CATEGORIES}
 
 

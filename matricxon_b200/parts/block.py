@@ -8,6 +8,9 @@ and each sub-layer adds into it in float.
 
 ``branch_norm_sequential``: ``x = x + s1 * norm1(mixer(x)); x = x + s2 * norm2(ffn(x))`` with learned vectors
 ``s1``, ``s2`` (optional), then whatever the layer adds from outside the stream (``LayerSpec.side_input``).
+
+``sandwich_norm_sequential``: ``x = x + norm1b(mixer(norm1(x))); x = x + norm2b(ffn(norm2(x)))``: a norm before and
+one after each sublayer.
 """
 
 from __future__ import annotations
@@ -228,6 +231,87 @@ class BranchNormSequentialBlock(Block):
         if self.side_input is not None:
             x, h = self.side_input.forward(x, h, ctx)
         ctx.memo["stream_activations"] = (x, h)
+        return x
+
+
+@register_part("block", "sandwich_norm_sequential")
+class SandwichNormSequentialBlock(Block):
+    """A norm on both sides of each sublayer: ``x = x + out_norm1(mixer(in_norm1(x)))``, then
+    ``x = x + out_norm2(ffn(in_norm2(x)))``; a layer without a feed-forward has only the first. The stream is float
+    and the sums are formed in float. The kernel that ends a sublayer (``Norm.forward_branch_add``) also forms the
+    next norm's output when that norm is known: the second sublayer's inside the block, and the next block's first
+    norm when the model names it (``ctx.next_input_norm``; the next block finds the rows in the step's memo under
+    ``normed_input``). Where nothing is known to follow, the new rows are left in the runtime dtype under
+    ``stream_activations`` for whoever reads the stream itself next."""
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        if spec.mixer_out_norm is None or (spec.feed_forward is not None and spec.ffn_out_norm is None):
+            raise ValueError("a sandwich block needs a norm behind every sublayer")
+        for norm in (spec.mixer_out_norm, spec.ffn_out_norm):
+            if norm is not None and not hasattr(part_class_of("norm", norm), "forward_branch_add"):
+                raise ValueError(f"norm {norm.kind!r} cannot end a branch (no forward_branch_add)")
+        sep = spec.part_separator
+        self.mixer_norm = build_part("norm", spec.mixer_norm, runtime, f"{prefix}{spec.mixer_norm_name}{sep}")
+        self.mixer = build_part("mixer", spec.mixer, runtime, f"{prefix}{spec.mixer_name}{sep}")
+        self.mixer_out_norm = build_part("norm", spec.mixer_out_norm, runtime, f"{prefix}{spec.mixer_out_norm_name}{sep}")
+        self.ffn_norm = self.feed_forward = self.ffn_out_norm = None
+        if spec.feed_forward is not None:
+            self.ffn_norm = build_part("norm", spec.ffn_norm, runtime, f"{prefix}{spec.ffn_norm_name}{sep}")
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, runtime,
+                                           f"{prefix}{spec.feed_forward_name}{sep}")
+            self.ffn_out_norm = build_part("norm", spec.ffn_out_norm, runtime, f"{prefix}{spec.ffn_out_norm_name}{sep}")
+        self.capturable = all(part.capturable for part in self.parts())
+
+    @property
+    def input_norm(self):
+        """The norm this block applies to the stream first (a block before it may apply it on its way out)."""
+        return self.mixer_norm
+
+    @classmethod
+    def weight_specs(cls, spec, prefix):
+        from matricxon_b200.parts.base import part_class
+
+        groups = [("norm", spec.mixer_norm, spec.mixer_norm_name), ("mixer", spec.mixer, spec.mixer_name),
+                  ("norm", spec.mixer_out_norm, spec.mixer_out_norm_name)]
+        if spec.feed_forward is not None:
+            groups += [("norm", spec.ffn_norm, spec.ffn_norm_name),
+                       ("feed_forward", spec.feed_forward, spec.feed_forward_name),
+                       ("norm", spec.ffn_out_norm, spec.ffn_out_norm_name)]
+        out = []
+        for category, sub, name in groups:
+            out.extend(part_class(category, sub.kind).weight_specs(sub, f"{prefix}{name}{spec.part_separator}"))
+        return out
+
+    def parts(self):
+        return tuple(part for part in (self.mixer_norm, self.mixer, self.mixer_out_norm, self.ffn_norm,
+                                       self.feed_forward, self.ffn_out_norm) if part is not None)
+
+    def load(self, fetch):
+        for part in self.parts():
+            part.load(fetch)
+
+    def forward(self, x, ctx, binding):
+        if isinstance(x, PendingSum):
+            x = x.tensor()
+        handed = ctx.memo.pop("normed_input", None)
+        if handed is not None and handed[0] is x and handed[1] is self.mixer_norm:
+            h = handed[2]                           # the block before applied this block's first norm on its way out
+        else:
+            h = self.mixer_norm.forward(x)
+        follower = getattr(ctx, "next_input_norm", None)
+        mixed = self.mixer.forward(h, None, ctx, binding)
+        last = self.mixer_out_norm
+        if self.feed_forward is not None:
+            x, h = self.mixer_out_norm.forward_branch_add(x, mixed, next_norm=self.ffn_norm)
+            mixed = self.feed_forward.forward(h, None, ctx)
+            last = self.ffn_out_norm
+        if follower is not None:
+            x, h = last.forward_branch_add(x, mixed, next_norm=follower)
+            ctx.memo["normed_input"] = (x, follower, h)
+        else:
+            x, h = last.forward_branch_add(x, mixed, want_activations=True)
+            ctx.memo["stream_activations"] = (x, h)
         return x
 
 

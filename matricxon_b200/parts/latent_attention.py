@@ -8,6 +8,11 @@ product after the softmax. A step is: one fused product (queries and the down pr
 result), one kernel that normalises the latent, rotates the rotated parts and stores the token's cache
 vector, the query-side per-head product, the attention kernel over the paged latent cache, the
 value-side per-head product, and the output projection. Scores, softmax, norm and angles are float.
+
+Optional, by the spec: queries through a latent of their own (the first product then gives the query latent, the
+down projection and the gate; an RMS norm and a second product give the queries), a learned sink logit per head in
+the softmax's denominator, a sigmoid gate on the concatenated heads that reads the mixer's input, and either
+pairing of the rotated entries.
 """
 
 from __future__ import annotations
@@ -37,13 +42,22 @@ class LatentAttention(Mixer):
     @classmethod
     def weight_specs(cls, spec, prefix):
         s = spec
-        matrices = {s.query_name: (s.num_heads * (s.head_dim + s.rot_dim), s.hidden_size),
+        q_rows = s.num_heads * (s.head_dim + s.rot_dim)
+        matrices = {s.query_name: (q_rows, s.hidden_size if s.query_rank is None else s.query_rank),
                     s.down_name: (s.latent_rank + s.rot_dim, s.hidden_size),
                     s.key_up_name: (s.num_heads * s.head_dim, s.latent_rank),
                     s.value_up_name: (s.num_heads * s.value_dim, s.latent_rank),
                     s.output_name: (s.hidden_size, s.num_heads * s.value_dim)}
         specs = [WeightSpec(prefix + name, shape, role="matrix", init="weight") for name, shape in matrices.items()]
         specs.append(WeightSpec(prefix + s.latent_norm_name, (s.latent_rank,), role="vector", init="norm_weight"))
+        if s.query_rank is not None:
+            specs.append(WeightSpec(prefix + s.query_down_name, (s.query_rank, s.hidden_size), role="matrix", init="weight"))
+            specs.append(WeightSpec(prefix + s.query_norm_name, (s.query_rank,), role="vector", init="norm_weight"))
+        if s.gate_name is not None:
+            specs.append(WeightSpec(prefix + s.gate_name, (s.num_heads * s.value_dim, s.hidden_size), role="matrix",
+                                    init="weight"))
+        if s.sink_name is not None:
+            specs.append(WeightSpec(prefix + s.sink_name, (s.num_heads,), role="vector", init="bias"))
         return specs
 
     @classmethod
@@ -54,7 +68,16 @@ class LatentAttention(Mixer):
 
     def load(self, fetch):
         p, s = self.prefix, self.spec
-        self.proj_weight = torch.cat([fetch(p + s.query_name), fetch(p + s.down_name)])
+        # rows of the product that reads the mixer's input: [queries or their latent | down projection | gate]
+        first = [fetch(p + (s.query_name if s.query_rank is None else s.query_down_name)), fetch(p + s.down_name)]
+        if s.gate_name is not None:
+            first.append(fetch(p + s.gate_name))
+        self.proj_weight = torch.cat(first)
+        self.query_up = self.query_norm = None
+        if s.query_rank is not None:
+            self.query_up = fetch(p + s.query_name)
+            self.query_norm = fetch(p + s.query_norm_name)
+        self.sink = fetch(p + s.sink_name) if s.sink_name is not None else None
         self.latent_norm = fetch(p + s.latent_norm_name)
         # Uk as [head][rank][dim]: the query-side product is q_plain_h @ Uk_h, i.e. "weight" Uk_h^T
         self.key_up_t = fetch(p + s.key_up_name).view(s.num_heads, s.head_dim, s.latent_rank) \
@@ -92,13 +115,24 @@ class LatentAttention(Mixer):
             raise RuntimeError("latent attention needs cache pages bound to it")
         n, heads, rank = h.shape[0], s.num_heads, s.latent_rank
         proj = linear(h, self.proj_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
+        interleaved = bool(getattr(self.position, "interleaved", False))
+        down = None
+        first_width = heads * (s.head_dim + s.rot_dim) if s.query_rank is None else s.query_rank
+        if s.query_rank is not None:
+            # the queries' own latent: normalised in float, then expanded to the heads (float result)
+            latent_q = torch.empty((n, s.query_rank), dtype=rt.dtype, device=h.device)
+            kernels.rmsnorm(proj, self.query_norm, 0.0, s.eps, latent_q)
+            down = proj[:, first_width:]
+            queries = linear(latent_q, self.query_up, None, EPILOGUE_F32, backend=rt.gemm_backend)
+        else:
+            queries = proj
         q_plain = torch.empty((n, heads * s.head_dim), dtype=rt.dtype, device=h.device)
         q_lat = torch.empty((n, heads, self.key_width), dtype=rt.dtype, device=h.device)
         writes = binding.writes
-        kernels.latent_prepare(proj, ctx.positions, self.position.frequencies, self.position.amplitude,
+        kernels.latent_prepare(queries, ctx.positions, self.position.frequencies, self.position.amplitude,
                                self.latent_norm, s.eps, ctx.groups[binding.group].slots if writes else None,
                                binding.kv if writes else None, q_plain, q_lat, heads, s.head_dim, s.rot_dim,
-                               s.position.rotary_dim, rank, ctx.status)
+                               s.position.rotary_dim, rank, ctx.status, down=down, interleaved=interleaved)
         batched_linear(q_plain.view(n, heads, s.head_dim), self.key_up_t, None, q_lat[:, :, :rank])
         mixed = torch.empty((n, heads, rank), dtype=rt.dtype, device=h.device)
         tables = ctx.groups[binding.group].block_tables
@@ -108,12 +142,17 @@ class LatentAttention(Mixer):
             few_rows = heads <= 16 and (ctx.padded or max(ctx.host.q_lens) * heads <= 16)
             kernels.latent_attention_mma(q_lat, binding.kv, tables, ctx.cu_q, ctx.context_lens, tiles, n_tiles, rank,
                                          s.window, s.scale, mixed, ctx.status, n_splits=n_splits, scratch=scratch,
-                                         few_rows=few_rows)
+                                         few_rows=few_rows, sink=self.sink)
         else:       # the 32-bit path, and sizes the tensor-core kernel does not take
             kernels.latent_attention(q_lat, binding.kv, tables, ctx.tok_seq, ctx.positions, rank, s.window,
-                                     s.scale, mixed, ctx.status)
+                                     s.scale, mixed, ctx.status, sink=self.sink)
         attn = torch.empty((n, heads * s.value_dim), dtype=rt.dtype, device=h.device)
         batched_linear(mixed, self.value_up, None, attn.view(n, heads, s.value_dim))
+        if s.gate_name is not None:
+            gate_col = first_width + rank + s.rot_dim
+            gated = torch.empty_like(attn)
+            kernels.sigmoid_gate(attn, proj[:, gate_col:gate_col + heads * s.value_dim], gated, heads, s.value_dim)
+            attn = gated
         if residual is None:
             return linear(attn, self.o_weight, None, EPILOGUE_F32, backend=rt.gemm_backend)
         return linear(attn, self.o_weight, None, EPILOGUE_RESIDUAL, residual=residual, out=residual,

@@ -77,6 +77,7 @@ class RmsNorm(Norm):
     def load(self, fetch):
         self.weight = fetch(self.prefix + self.spec.weight_name)
         self.offset = 1.0 if self.spec.unit_offset else 0.0
+        self.scale = self.weight + 1.0 if self.spec.unit_offset else self.weight      # what a row is multiplied with
 
     def forward(self, x, out=None, rows=None):
         n_rows = x.shape[0] if rows is None else rows.numel()
@@ -94,6 +95,29 @@ class RmsNorm(Norm):
         act = torch.empty(tuple(x.shape), dtype=self.runtime.dtype, device=x.device)
         kernels.rmsnorm_sum(x, sublayer, skip_scale, self.weight, self.offset, self.spec.eps, act)
         return x, act
+
+
+    def forward_branch_add(self, x, branch, next_norm=None, want_activations=False):
+        """``x <- x + norm(branch)`` in place (both float32): the end of a sublayer whose own output is normalised
+        before it joins the stream. Returns (x, activations): with ``next_norm`` (another ``RmsNorm`` of the same
+        size) the rows ``next_norm(x)`` in the runtime dtype, formed by the same kernel; else, with
+        ``want_activations``, the new rows of ``x`` in the runtime dtype (``x`` itself on the 32-bit path); else
+        None."""
+        dtype = self.runtime.dtype
+        if next_norm is not None and (not isinstance(next_norm, RmsNorm) or next_norm.spec.eps != self.spec.eps
+                                      or next_norm.spec.size != self.spec.size):
+            kernels.rmsnorm_branch_add(x, branch, self.scale, None, None, self.spec.eps)
+            return x, next_norm.forward(x)
+        if next_norm is not None:
+            out = torch.empty(tuple(x.shape), dtype=dtype, device=x.device)
+            kernels.rmsnorm_branch_add(x, branch, self.scale, next_norm.scale, out, self.spec.eps)
+            return x, out
+        if want_activations and dtype != torch.float32:
+            out = torch.empty(tuple(x.shape), dtype=dtype, device=x.device)
+            kernels.rmsnorm_branch_add(x, branch, self.scale, None, out, self.spec.eps)
+            return x, out
+        kernels.rmsnorm_branch_add(x, branch, self.scale, None, None, self.spec.eps)
+        return x, (x if want_activations else None)
 
 
 @register_part("norm", "dynamic_tanh")

@@ -142,3 +142,27 @@ class WavelengthScaledRotary(PositionEncoding):
 
     def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim):
         raise NotImplementedError("a wavelength-scaled table serves mixers that rotate in their own kernels")
+
+
+def paired_frequencies(spec) -> torch.Tensor:
+    """Radians per position of every pair of a ``PairedRotarySpec``: ``theta^(-2i/D)``, in float64 on the host."""
+    dims = spec.rotary_dim
+    return torch.tensor([spec.theta ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=torch.float64)
+
+
+@register_part("position", "rotary_paired")
+class PairedRotary(PositionEncoding):
+    """Holds the frequency table (``frequencies``, float32 on the device) and the pairing (``interleaved``) of a
+    ``PairedRotarySpec`` for mixers whose own kernels rotate a part of each head; angles are
+    ``position * frequency`` in float there. ``amplitude`` is 1: cos and sin are used as they are."""
+
+    capturable = True
+    amplitude = 1.0
+
+    def __init__(self, spec, runtime, prefix):
+        super().__init__(spec, runtime, prefix)
+        self.frequencies = paired_frequencies(spec).to(torch.float32).to(runtime.device)
+        self.interleaved = spec.pairing == "interleaved"
+
+    def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim):
+        raise NotImplementedError("a paired rotary table serves mixers that rotate in their own kernels")

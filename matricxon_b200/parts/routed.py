@@ -14,7 +14,8 @@ second weighs every pair's row). The experts' matrices are stacked at load: ``[e
 ``[experts, hidden, ff]``. The router's matrix is held in float.
 
 ``score="softmax"`` routes by another rule (softmax over all router rows, a correction that moves the choice and not
-the weights) and may name experts without matrices that return their input: such a pair takes no row of the grouped
+the weights; optionally a bias on the logits themselves, which makes the rule "the largest logits, weighted by the
+softmax over the chosen ones") and may name experts without matrices that return their input: such a pair takes no row of the grouped
 products, and the combining kernel adds ``weight * h`` for it. An expert may be a ``GatedMlpSpec`` or a
 ``ClampedGluSpec`` (the activation differs). A ``shared`` feed-forward runs for every token; the routed sum is added
 onto its output.
@@ -63,6 +64,8 @@ class RoutedExperts(FeedForward):
         specs.append(WeightSpec(prefix + spec.router_name, (rows, spec.hidden_size), role="vector", init="weight"))
         if spec.correction_name is not None:
             specs.append(WeightSpec(prefix + spec.correction_name, (rows,), role="vector", init="bias"))
+        if spec.bias_name is not None:
+            specs.append(WeightSpec(prefix + spec.bias_name, (rows,), role="vector", init="bias"))
         if spec.shared is not None:
             specs += part_class("feed_forward", spec.shared.kind).weight_specs(spec.shared, prefix + spec.shared_name)
         return specs
@@ -74,6 +77,7 @@ class RoutedExperts(FeedForward):
         self.down = torch.stack([fetch(q + e.down_name) for q in names])
         self.router = fetch(self.prefix + s.router_name)
         self.correction = fetch(self.prefix + s.correction_name) if s.correction_name is not None else None
+        self.bias = fetch(self.prefix + s.bias_name) if s.bias_name is not None else None
         if self.shared is not None:
             self.shared.load(fetch)
 
@@ -96,7 +100,8 @@ class RoutedExperts(FeedForward):
             counts.zero_()
         weights = torch.empty(n_pairs, dtype=torch.float32, device=device)
         if s.score == "softmax":
-            kernels.moe_route_softmax(h, self.router, s.top, s.num_identity, self.correction, ids, weights, counts, place)
+            kernels.moe_route_softmax(h, self.router, s.top, s.num_identity, self.correction, ids, weights, counts, place,
+                                      bias=self.bias)
         else:
             kernels.moe_route(h, self.router, s.top, s.num_groups, s.groups_kept, s.route_scale, ids, weights, counts,
                               place)

@@ -136,7 +136,13 @@ class LatentAttentionSpec:
     entries (RMS-normalised with a plain weight: the latent) and ``rot_dim`` more (one rotated key
     part shared by all heads). Head h's plain key is ``Uk_h latent``, its value ``Uv_h latent``
     (``value_dim`` wide); scores are ``(q_plain . k_plain + q_rot . k_rot) * scale`` under the window
-    rule of ``AttentionSpec``. Names are full tensor names under the mixer's prefix."""
+    rule of ``AttentionSpec``. Names are full tensor names under the mixer's prefix.
+
+    ``query_rank`` set: the queries go through a latent of their own, ``q = Uq n(Dq h)`` with ``n`` an RMS norm
+    with a plain weight (``query_down_name``, ``query_norm_name``; ``query_name`` is then Uq, [heads * (head_dim +
+    rot_dim), query_rank]). ``sink_name``: a learned logit per head that joins the softmax's denominator without a
+    value. ``gate_name``: the concatenated heads are multiplied entry by entry with ``sigmoid(G h)`` before the
+    output projection. The rotation pairs entries as ``position`` says."""
 
     hidden_size: int
     num_heads: int
@@ -154,6 +160,11 @@ class LatentAttentionSpec:
     key_up_name: str
     value_up_name: str
     output_name: str
+    query_rank: int | None = None
+    query_down_name: str | None = None
+    query_norm_name: str | None = None
+    sink_name: str | None = None
+    gate_name: str | None = None
     kind: str = "latent_attention"
 
     def __post_init__(self) -> None:
@@ -161,6 +172,9 @@ class LatentAttentionSpec:
             raise ValueError("latent attention needs positive head count, head sizes and latent rank")
         if self.position is not None and self.position.rotary_dim > self.rot_dim:
             raise ValueError(f"{self.position.rotary_dim} rotated dimensions exceed the rotated part of {self.rot_dim}")
+        if self.query_rank is not None and (self.query_rank <= 0 or self.query_down_name is None
+                                            or self.query_norm_name is None):
+            raise ValueError("queries through a latent need its positive rank and the names of its projection and norm")
 
 
 @dataclass(frozen=True)
@@ -393,6 +407,101 @@ class SinkAttentionSpec:
 
 
 @dataclass(frozen=True)
+class PairedRotarySpec:
+    """Rotary encoding of the first ``rotary_dim`` entries of a head with plain frequencies
+    ``f_i = theta^(-2i/rotary_dim)``. ``pairing`` says which entries turn together: ``"half"`` pairs entry i with
+    entry i + rotary_dim/2, ``"interleaved"`` pairs entry 2i with entry 2i + 1 (i < rotary_dim/2). The pair
+    ``(u, v)`` at position p becomes ``(u cos a - v sin a, v cos a + u sin a)`` with ``a = p f_i``."""
+
+    rotary_dim: int
+    theta: float
+    pairing: str = "half"
+    kind: str = "rotary_paired"
+
+    def __post_init__(self) -> None:
+        if self.rotary_dim < 0 or self.rotary_dim % 2:
+            raise ValueError(f"a rotary encoding pairs dimensions: {self.rotary_dim} is odd or negative")
+        if self.pairing not in ("half", "interleaved"):
+            raise ValueError(f"pairing is 'half' or 'interleaved', not {self.pairing!r}")
+        if not self.theta > 0:
+            raise ValueError(f"the rotary base must be positive, got {self.theta}")
+
+
+@dataclass(frozen=True)
+class NormedRotaryAttentionSpec:
+    """Grouped-query attention without biases whose queries and keys are RMS-normalised head by head (one plain
+    weight of ``head_dim`` entries for all query heads, one for all key heads; a name of None: no norm) and THEN
+    rotated over their first entries (``position``, a ``PairedRotarySpec``; None: no rotation). Scores are
+    ``q . k * scale``, optionally capped to ``softcap * tanh(score / softcap)``; values are ``value_dim`` wide.
+
+    ``mask`` names the rule beside ``j <= p``: ``"causal"`` (nothing more), ``"window"`` (``p - j < mask_size``) or
+    ``"chunk"`` (``p // mask_size == j // mask_size``: the sequence is cut into blocks of ``mask_size`` positions
+    counted from its start, and a query sees its own block only). ``sink``: ``None`` for the ordinary softmax,
+    ``"zero"`` for a denominator with one added (a logit of 0 without a value), ``"learned"`` for a learned logit
+    per head (``sink_name``). ``gate``: ``None``, ``"head"`` (head h times ``sigmoid(G h)_h``, G has one row per head)
+    or ``"entry"`` (the concatenated heads times ``sigmoid(G h)`` entry by entry); the gate reads the mixer's input."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    eps: float
+    position: Any | None
+    query_name: str
+    key_name: str
+    value_name: str
+    output_name: str
+    mask: str = "causal"
+    mask_size: int = 0
+    softcap: float | None = None
+    sink: str | None = None
+    sink_name: str | None = None
+    gate: str | None = None
+    gate_name: str | None = None
+    query_norm_name: str | None = None
+    key_norm_name: str | None = None
+    kind: str = "normed_rotary_attention"
+
+    def __post_init__(self) -> None:
+        if self.num_kv_heads <= 0 or self.num_heads % self.num_kv_heads != 0:
+            raise ValueError(f"{self.num_heads} attention heads are no multiple of {self.num_kv_heads} kv heads")
+        if self.head_dim <= 0 or self.value_dim <= 0 or max(self.head_dim, self.value_dim) > 256:
+            raise ValueError(f"head sizes {self.head_dim} / {self.value_dim} are outside 1..256: "
+                             "no attention kernel of this engine takes them")
+        if self.mask not in ("causal", "window", "chunk"):
+            raise ValueError(f"mask is 'causal', 'window' or 'chunk', not {self.mask!r}")
+        if self.mask != "causal" and self.mask_size <= 0:
+            raise ValueError(f"a {self.mask} mask needs a positive size, got {self.mask_size}")
+        if self.sink not in (None, "zero", "learned") or (self.sink == "learned" and self.sink_name is None):
+            raise ValueError("sink is None, 'zero' or 'learned' (with the tensor's name)")
+        if self.gate not in (None, "head", "entry") or (self.gate is not None and self.gate_name is None):
+            raise ValueError("gate is None, 'head' or 'entry' (with the tensor's name)")
+        if self.position is not None and self.position.rotary_dim > self.head_dim:
+            raise ValueError(f"{self.position.rotary_dim} rotated entries exceed the head of {self.head_dim}")
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"a score cap must be positive, got {self.softcap}")
+
+
+@dataclass(frozen=True)
+class ReinjectionSpec:
+    """What a model does to the stream before every pass of a repeated run of layers: with x0 the embedding output
+    of the step's tokens, ``x <- M [x; x0] + s_t`` for pass t, where M is ``[hidden, 2 hidden]`` (the stream's columns
+    first) and s is ``[passes, hidden]``. Full tensor names."""
+
+    hidden_size: int
+    passes: int
+    matrix_name: str
+    step_name: str
+    kind: str = "reinjection"
+
+    def __post_init__(self) -> None:
+        if self.passes <= 0:
+            raise ValueError(f"a repeated run has at least one pass, got {self.passes}")
+
+
+@dataclass(frozen=True)
 class GlaSpec:
     """Gated linear attention: per head a state ``S <- diag(a_t) S + k_t v_t^T`` from S = 0 and ``o_t = S^T q_t``
     with ``q = Wq h * query_scale``, ``k = Wk h`` (``head_dim`` wide), ``v = Wv h`` (``value_dim`` wide) and a decay
@@ -455,7 +564,9 @@ class RoutedExpertsSpec:
     plain scores; there are no groups and no ``route_scale``. The router then has ``num_experts + num_identity``
     rows, the last ``num_identity`` of which stand for experts without tensors whose output is their input.
     ``expert`` may be a ``GatedMlpSpec`` or a ``ClampedGluSpec``. ``shared`` (a feed-forward spec, tensors under
-    ``<prefix><shared_name>``) runs for every token and is added."""
+    ``<prefix><shared_name>``) runs for every token and is added. With ``bias_name`` the logits are ``R h + b``; the
+    softmax rule with such a bias and without a correction is the same as choosing the ``top`` largest logits and
+    weighting them by the softmax over the chosen logits alone."""
 
     hidden_size: int
     num_experts: int
@@ -470,6 +581,7 @@ class RoutedExpertsSpec:
     norm_eps: float = 1e-20
     score: str = "sigmoid"
     correction_name: str | None = None
+    bias_name: str | None = None          # softmax rule: a float per router row added to the logits themselves
     num_identity: int = 0
     shared: Any | None = None
     shared_name: str = "shared."
@@ -480,8 +592,10 @@ class RoutedExpertsSpec:
             raise ValueError(f"router scores are 'sigmoid' or 'softmax', not {self.score!r}")
         if self.num_identity < 0 or self.num_experts < 0:
             raise ValueError("expert counts cannot be negative")
-        if self.score == "sigmoid" and (self.num_identity or self.correction_name is not None):
-            raise ValueError("experts without tensors and a correction of the choice belong to the softmax rule")
+        if self.score == "sigmoid" and (self.num_identity or self.correction_name is not None
+                                        or self.bias_name is not None):
+            raise ValueError("experts without tensors, a correction of the choice and a bias on the logits belong "
+                             "to the softmax rule")
         if self.score == "softmax" and (self.num_groups != 1 or self.route_scale != 1.0):
             raise ValueError("the softmax rule has neither groups nor a scale of its weights")
         if not 0 < self.top <= self.num_experts + self.num_identity:
@@ -523,6 +637,12 @@ class LayerSpec:
     # what the layer adds to the stream after its sublayers (``TokenSideInputSpec``; None: nothing) and its fragment
     side_input: Any | None = None
     side_input_name: str = ""
+    # blocks that normalise a sublayer's output as well as its input: the norms behind the mixer and behind the
+    # feed-forward and their name fragments
+    mixer_out_norm: Any | None = None
+    ffn_out_norm: Any | None = None
+    mixer_out_norm_name: str = ""
+    ffn_out_norm_name: str = ""
     # what the pre-norm block puts behind a part's name fragment to make its prefix ("" for checkpoints whose
     # fragments carry their own separators, as the post-norm block expects them)
     part_separator: str = "."
@@ -540,6 +660,9 @@ class ScheduleEntry:
 
     layer: int
     cache_of: int | None = None
+    # the entry opens pass number ``pass_index`` of a repeated run of layers: the model's ``pass_input`` part
+    # transforms the stream right before it (None: nothing happens before the entry)
+    pass_index: int | None = None
 
 
 @dataclass(frozen=True)
@@ -564,6 +687,8 @@ class ModelSpec:
     head_bias: bool = False
     logit_softcap: float | None = None
     logit_scale: float = 1.0             # logits times a constant
+    # what happens to the stream before the schedule entries that open a pass (``ReinjectionSpec``; None: nothing)
+    pass_input: Any | None = None
     # how names are put together: "<embedding_name><weight_suffix>", a layer's prefix from
     # ``layer_prefix_format`` (fields {prefix} and {index}), the final norm's prefix (None:
     # "<final_norm_name>.")
@@ -574,6 +699,8 @@ class ModelSpec:
 
     def __post_init__(self) -> None:
         for position, entry in enumerate(self.schedule):
+            if entry.pass_index is not None and self.pass_input is None:
+                raise ValueError(f"schedule entry {position} opens a pass, but the model describes no pass input")
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"schedule entry {position} names layer {entry.layer}, "
                                  f"but the model has {len(self.layers)} layers")
