@@ -121,8 +121,10 @@ class KefasunLayer:
         heads, dim = m.integer("heads", minimum=1), m.integer("dim", minimum=1)
         fields: dict[str, Any] = {"type": kind, "heads": heads, "dim": dim, "vdim": m.integer("vdim", dim, minimum=1),
                                   "scale": m.number("scale", positive=True)}
-        rot = ConfigReader(_object(mixer, "rot", where + ".mixer"), where + ".mixer.rot")
-        fields["rot_dims"], fields["rot_base"] = rot.integer("dims", minimum=0), rot.number("base", positive=True)
+        fields["rot_dims"], fields["rot_base"] = 0, 10000.0             # no 'rot': nothing is rotated
+        if mixer.get("rot") is not None:
+            rot = ConfigReader(_object(mixer, "rot", where + ".mixer"), where + ".mixer.rot")
+            fields["rot_dims"], fields["rot_base"] = rot.integer("dims", minimum=0), rot.number("base", positive=True)
         if fields["rot_dims"] % 2:
             raise ConfigError(f"{where}.mixer.rot: 'dims' must be even, got {fields['rot_dims']}")
         if kind == "latent_attention":
@@ -139,25 +141,26 @@ class KefasunLayer:
             if max(dim, fields["vdim"]) > 256:
                 raise ConfigError(f"{where}.mixer: head sizes above 256 have no attention kernel")
             fields["kv_heads"] = kv_heads
-        if kind != "attention_2":
+        if kind != "attention_2" and mixer.get("mask") is not None:    # no 'mask': every earlier key is seen
             mask = ConfigReader(_object(mixer, "mask", where + ".mixer"), where + ".mixer.mask")
             fields["mask_size"] = mask.integer("size", minimum=1)
-        else:
+        if kind == "attention_2":
             fields["softcap"] = m.number("softcap", positive=True)
         if raw.get("mlp") is not None:
             fields["feed_forward"] = KefasunFeedForward.from_dict(raw["mlp"], where + ".mlp")
         return cls(**fields)
 
     def to_dict(self) -> dict:
-        mixer: dict[str, Any] = {"dim": self.dim, "heads": self.heads, "rot": {"base": self.rot_base, "dims": self.rot_dims},
-                                 "scale": self.scale, "vdim": self.vdim}
+        mixer: dict[str, Any] = {"dim": self.dim, "heads": self.heads, "scale": self.scale, "vdim": self.vdim}
+        if self.rot_dims:
+            mixer["rot"] = {"base": self.rot_base, "dims": self.rot_dims}
         if self.type == "latent_attention":
             mixer.update({"kv_rank": self.kv_rank, "q_rank": self.q_rank, "rot_dim": self.rot_dim})
         else:
             mixer["kv_heads"] = self.kv_heads
         if self.type == "attention_2":
             mixer["softcap"] = self.softcap
-        else:
+        elif self.mask_size:
             mixer["mask"] = {"size": self.mask_size}
         return {"mixer": mixer, "mlp": self.feed_forward.to_dict() if self.feed_forward else None, "type": self.type}
 
@@ -260,13 +263,14 @@ class KefasunConfig:
                 raise ConfigError(f"{where}.mixer: 'q_rank' and 'kv_rank' are needed (config.json or the tensors give them)")
             return LatentAttentionSpec(
                 hidden_size=self.width, num_heads=layer.heads, head_dim=layer.dim, rot_dim=layer.rot_dim,
-                value_dim=layer.vdim, latent_rank=layer.kv_rank, window=layer.mask_size, scale=layer.scale,
+                value_dim=layer.vdim, latent_rank=layer.kv_rank, window=layer.mask_size or None, scale=layer.scale,
                 eps=self.eps, position=PairedRotarySpec(rotary_dim=layer.rot_dims, theta=layer.rot_base,
                                                         pairing="interleaved"),
                 query_name="uq", down_name="dkv", latent_norm_name="dkv.norm", key_up_name="uk", value_up_name="uv",
                 output_name="o", query_rank=layer.q_rank, query_down_name="dq", query_norm_name="dq.norm",
                 sink_name="sink", gate_name="g")
         first = layer.type == "attention"
+        blocks = first and layer.mask_size > 0
         position = None
         if layer.rot_dims > 0:
             position = PairedRotarySpec(rotary_dim=layer.rot_dims, theta=layer.rot_base,
@@ -274,8 +278,8 @@ class KefasunConfig:
         return NormedRotaryAttentionSpec(
             hidden_size=self.width, num_heads=layer.heads, num_kv_heads=layer.kv_heads, head_dim=layer.dim,
             value_dim=layer.vdim, scale=layer.scale, eps=self.eps, position=position, query_name="q", key_name="k",
-            value_name="v", output_name="o", mask="chunk" if first else "causal",
-            mask_size=layer.mask_size if first else 0, softcap=None if first else layer.softcap,
+            value_name="v", output_name="o", mask="chunk" if blocks else "causal",
+            mask_size=layer.mask_size if blocks else 0, softcap=None if first else layer.softcap,
             sink="zero" if first else None, gate="head" if first else "entry", gate_name="g",
             query_norm_name="q.norm", key_norm_name="k.norm")
 

@@ -152,14 +152,18 @@ def route(h, router, bias, top):
     return chosen, weights, margin
 
 
-def feed_forward(h, w, p, f, forced=None):
+def feed_forward(h, w, p, f, forced=None, heard=None):
     """``f``: the layer's ``mlp`` config. ``forced`` [T, top]: expert choices to use instead of the router's own
-    (weights are still the softmax over those experts' logits)."""
+    (weights are still the softmax over those experts' logits). ``heard``: a list that receives (the router's own
+    choice, its margin) of a routed layer."""
     if f["kind"] == "dense":
         return silu_glu(h, w[p + "gate"], w[p + "up"], w[p + "down"])
     top = f["router"]["top"]
     z = h @ w[p + "router"].T + w[p + "router.b"]
-    chosen = route(h, w[p + "router"], w[p + "router.b"], top)[0] if forced is None else forced.long()
+    own, _, margin = route(h, w[p + "router"], w[p + "router.b"], top)
+    if heard is not None:
+        heard.append((own, margin))
+    chosen = own if forced is None else torch.as_tensor(forced).long()
     weights = torch.softmax(torch.gather(z, 1, chosen), dim=-1)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
@@ -184,8 +188,15 @@ def layer_order(config):
     return order + [(i, None) for i in range(stop, n)]
 
 
-def forward(config, w, tokens, return_layers=False, forced=None):
-    """Logits [T, vocab] of one sequence. ``forced``: {layer-run index: [T, top] expert choices}."""
+def routed_runs(config):
+    """The layer runs (indices into ``layer_order``) whose layer has routed experts, in order."""
+    return [run for run, (i, _) in enumerate(layer_order(config))
+            if (config["layers"][i].get("mlp") or {}).get("kind") == "moe"]
+
+
+def forward(config, w, tokens, return_layers=False, forced=None, heard=None):
+    """Logits [T, vocab] of one sequence. ``forced``: {layer-run index: [T, top] expert choices}; ``heard``: a list
+    that receives (own choice, margin) of every routed layer run."""
     eps = config["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)].to(F64)
     x0 = x.clone()
@@ -199,7 +210,7 @@ def forward(config, w, tokens, return_layers=False, forced=None):
                          w[p + "norm1b"], eps)
         if layer.get("mlp") is not None:
             fed = feed_forward(rms_norm(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"],
-                               None if forced is None else forced.get(run))
+                               None if forced is None else forced.get(run), heard)
             x = x + rms_norm(fed, w[p + "norm2b"], eps)
         taps.append(x.clone())
     logits = (rms_norm(x, w["final.norm"], eps) @ w["embed"].T) * config.get("logit_scale", 1.0)

@@ -1,0 +1,762 @@
+"""Kefasun through the engine against the plain implementation (tests/plain_kefasun.py): every mechanism alone,
+then whole models cut and batched every way, in float32 and bfloat16, with pools so small that pages and slots
+are used again. Sizes, orders and constants are the tests' own."""
+
+import copy
+import json
+import math
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_kefasun as plain
+from kefasun_configs import MODELS, blocks, capped, dense, draw, ids, latent, moe, single_layer
+from matricxon_b200.config.registry import config_from_dict
+from matricxon_b200.engine.core import model_from_tensors
+from matricxon_b200.engine.replay import TraceReplayer
+from matricxon_b200.ops import kernels
+from trace_utils import ROOT
+
+pytestmark = pytest.mark.gpu
+
+DEVICE = "cuda:0"
+CHUNKS = [7, 2, 5, 3, 11, 2, 4, 13, 2, 9]
+F64 = torch.float64
+
+
+def limit_for(dtype: str, reference: np.ndarray) -> float:
+    scale = max(1.0, float(np.abs(reference).max()))
+    return (2e-4 if dtype == "float32" else 0.06) * scale
+
+
+def rounded(tensors: dict, dtype: str) -> dict:
+    """What the engine holds: a bfloat16 engine reads bfloat16 matrices, so the plain side gets the same."""
+    if dtype == "float32":
+        return tensors
+    return {name: value.to(torch.bfloat16).float() for name, value in tensors.items()}
+
+
+def doubles(tensors: dict) -> dict:
+    return {name: value.double() for name, value in tensors.items()}
+
+
+class Run:
+    """One engine over one model: requests fed in portions, logits kept per (request, position).
+
+    A bfloat16 engine may send a token to another expert than the plain model does when two router logits lie
+    closer than 16-bit rounding resolves, and the positions that attend to such a token differ then too. That is no
+    fault, so the bfloat16 runs listen to the engine's choices (``StepRunner.taps``; such steps run launch by launch)
+    and hand them to the plain model, which is then compared at every position; where the plain model's own choice is
+    clear, the engine's is the same but for one in fifty. float32 runs listen to nothing, replay captured steps and
+    are compared with the plain model's own routing."""
+
+    clear = unclear = 0
+
+    def __init__(self, raw: dict, tensors: dict, dtype: str, max_tokens: int, max_requests: int = 4,
+                 page_size: int = 16) -> None:
+        self.raw, self.dtype = raw, dtype
+        self.weights = rounded(tensors, dtype)
+        self.plain_weights = doubles(self.weights)
+        config = config_from_dict(copy.deepcopy(raw))
+        model = model_from_tensors(config, self.weights, dtype=dtype, device=DEVICE, page_size=page_size)
+        self.replayer = TraceReplayer(None, dtype, max_tokens, page_size=page_size, device=DEVICE,
+                                      max_requests=max_requests, model=model, poison_cache=True)
+        self.routed = plain.routed_runs(raw)
+        self.listens = dtype == "bfloat16" and bool(self.routed)
+        if self.listens:
+            self.replayer.core.runner.taps = ("expert_choices",)
+        self.logits: dict[tuple[str, int], np.ndarray] = {}
+        self.choices: dict[tuple[str, int], list] = {}
+        self.progress: dict[str, int] = {}
+        self.slots_seen: dict[str, int] = {}
+
+    def step(self, portions: list[tuple[str, list[int]]], end=()) -> None:
+        entries, keys = [], []
+        for request, tokens in portions:
+            start = self.progress.get(request, 0)
+            entries.append({"id": request, "tokens": tokens, "want": list(range(len(tokens)))})
+            keys.extend((request, start + i) for i in range(len(tokens)))
+            self.progress[request] = start + len(tokens)
+        out = self.replayer.step(entries, [])
+        rows = list(self.replayer.last_rows)
+        if self.listens:
+            heard = [layer.cpu() for layer in self.replayer.core.runner.last_taps["expert_choices"]]
+            assert len(heard) == len(self.routed)
+            for row, key in enumerate(keys):
+                self.choices[key] = [layer[row].tolist() for layer in heard]
+        for request, _ in portions:
+            self.slots_seen[request] = self.replayer.core.cache.record(request).state_slot
+        if end:
+            self.replayer.step([], list(end))
+            for request in end:
+                self.progress.pop(request, None)
+        assert rows == keys
+        for key, row in zip(keys, out.numpy()):
+            self.logits[key] = row
+        self.replayer.core.cache.check_invariants()
+
+    def feed(self, request: str, tokens: list[int], sizes, end: bool = True) -> None:
+        """One request alone, cut into portions of the given sizes (a list, then one by one; or a function of
+        the turn)."""
+        start, turn = 0, 0
+        while start < len(tokens):
+            if isinstance(sizes, list):
+                size = sizes[turn] if turn < len(sizes) else 1
+            else:
+                size = sizes(turn)
+            size = min(size, len(tokens) - start)
+            turn += 1
+            last = start + size == len(tokens)
+            self.step([(request, tokens[start:start + size])], end=[request] if last and end else [])
+            start += size
+
+    def check(self, request: str, tokens: list[int], first: int = 0) -> None:
+        forced, heard = None, []
+        if self.listens:
+            forced = {run: [self.choices[(request, i)][k] for i in range(len(tokens))]
+                      for k, run in enumerate(self.routed)}
+        want = plain.forward(self.raw, self.plain_weights, tokens, forced=forced, heard=heard).numpy()
+        if self.listens:
+            # under the engine's routing the plain model's stream is the engine's: where its own choice there is
+            # clear, it is the engine's
+            for k, (own, margin) in enumerate(heard):
+                clear = np.nonzero(margin.numpy() > 0.6)[0]
+                Run.clear += len(clear)
+                Run.unclear += len(tokens) - len(clear)
+                theirs = forced[self.routed[k]]
+                same = sum(sorted(own[t].tolist()) == sorted(theirs[t]) for t in clear)
+                assert same >= len(clear) - max(1, len(clear) // 50), (request, k, same, len(clear))
+        got = np.stack([self.logits[(request, i)] for i in range(first, len(tokens))])
+        worst = np.abs(got - want[first:]).max(axis=1)
+        limit = limit_for(self.dtype, want)
+        bad = np.nonzero(~(worst <= limit))[0]
+        assert bad.size == 0, (f"{request}: first wrong position {first + bad[0]} of {len(tokens)}, "
+                               f"error {worst[bad[0]]:.3e} > {limit:.1e}; {bad.size} positions over")
+
+
+def cycle(turn: int) -> int:
+    return CHUNKS[turn % len(CHUNKS)]
+
+
+# ---------------------------------------------------------------------- kernels alone
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden, rows", [(40, 9), (96, 3), (1002, 70), (4100, 5), (9000, 2)])
+def test_branch_add_norm_kernel(dtype, hidden, rows):
+    """x += unit(branch) * wb, then the next norm of the new x (or its rounding, or nothing) in the same kernel."""
+    torch.manual_seed(hidden)
+    x = torch.randn(rows, hidden, device=DEVICE) * 3
+    branch = torch.randn(rows, hidden, device=DEVICE) * 40 + 5.0
+    wb, wn = torch.randn(hidden, device=DEVICE), torch.randn(hidden, device=DEVICE)
+    want_x = x.double() + plain.rms_norm(branch.double(), wb.double(), 1e-3)
+    for mode in ("next", "round", "none"):
+        stream = x.clone()
+        out = None if mode == "none" else torch.empty(rows, hidden, dtype=dtype, device=DEVICE)
+        kernels.rmsnorm_branch_add(stream, branch, wb, wn if mode == "next" else None, out, 1e-3)
+        assert torch.allclose(stream.double(), want_x, rtol=1e-5, atol=1e-5), (stream.double() - want_x).abs().max()
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        if mode == "next":
+            want = plain.rms_norm(want_x, wn.double(), 1e-3)
+            assert torch.allclose(out.double(), want, rtol=tol, atol=tol)
+        elif mode == "round":
+            assert torch.equal(out, stream.to(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_of_the_first_columns_of_wider_rows(dtype):
+    torch.manual_seed(5)
+    wide = torch.randn(11, 200, device=DEVICE) * 2
+    weight = torch.randn(72, device=DEVICE)
+    out = torch.empty(11, 72, dtype=dtype, device=DEVICE)
+    kernels.rmsnorm(wide[:, :72], weight, 0.0, 1e-4, out)
+    want = plain.rms_norm(wide[:, :72].double(), weight.double(), 1e-4)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert torch.allclose(out.double(), want, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("heads, kv, dim, vdim, rot", [(6, 3, 24, 40, 12), (4, 1, 40, 8, 40), (3, 3, 16, 16, 0),
+                                                       (2, 2, 64, 64, 64), (2, 1, 128, 64, 32), (5, 5, 12, 20, 6),
+                                                       (1, 1, 200, 256, 100)])
+def test_norm_then_rotation_and_cache_write_kernel(dtype, interleaved, heads, kv, dim, vdim, rot):
+    """q and k normalised per head with a weight, then rotated over their first entries in either pairing; k and v
+    land in the pages their slots name, padded with zeros to the common head size; large positions keep their
+    angles."""
+    gen = torch.Generator().manual_seed(dim * 3 + vdim)
+    n, page = 11, 4
+    hd = -(-max(dim, vdim) // 16) * 16
+    width = (heads + kv) * dim + kv * vdim + 5
+    proj = torch.randn(n, width, generator=gen) * 2
+    positions = torch.tensor([0, 1, 2, 3, 50, 51, 1000, 4097, 20000, 7, 8], dtype=torch.int32)
+    wq, wk = torch.randn(dim, generator=gen), torch.randn(dim, generator=gen)
+    base = 10000.0
+    freq = torch.tensor([base ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float64).float()
+    n_pages = 9
+    slots = torch.randperm(n_pages * page, generator=gen)[:n].to(torch.int32)
+    slots[3] = -1                                                       # a padding row stores nothing
+    cache = torch.full((n_pages, 2, kv, page, hd), 7.0, dtype=dtype, device=DEVICE)
+    q_out = torch.empty(n, heads * hd, dtype=dtype, device=DEVICE)
+    status = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+    kernels.norm_rotate_kv_write(proj.to(DEVICE), positions.to(DEVICE), freq.to(DEVICE), rot, interleaved, wq.to(DEVICE),
+                                 wk.to(DEVICE), 1e-4, slots.to(DEVICE), cache, q_out, heads, kv, dim, vdim, status)
+    assert int(status.item()) == 0
+    layout = "interleaved" if interleaved else "half"
+    p64 = proj.double()
+    q = plain.rotate(plain.rms_norm(p64[:, :heads * dim].view(n, heads, dim), wq.double(), 1e-4), positions, rot, base, layout)
+    k = plain.rotate(plain.rms_norm(p64[:, heads * dim:(heads + kv) * dim].view(n, kv, dim), wk.double(), 1e-4),
+                     positions, rot, base, layout)
+    v = p64[:, (heads + kv) * dim:(heads + kv) * dim + kv * vdim].view(n, kv, vdim)
+    # float angles at positions in the thousands are good to about 1e-3 radians
+    tol = 4e-3 if dtype == torch.float32 else 3e-2
+    got_q = q_out.double().cpu().view(n, heads, hd)
+    assert torch.allclose(got_q[:, :, :dim], q, rtol=tol, atol=tol), (got_q[:, :, :dim] - q).abs().max()
+    assert float(got_q[:, :, dim:].abs().max()) == 0.0 if hd > dim else True
+    host = cache.double().cpu()
+    for t in range(n):
+        if slots[t] < 0:
+            continue
+        pg, off = int(slots[t]) // page, int(slots[t]) % page
+        assert torch.allclose(host[pg, 0, :, off, :dim], k[t], rtol=tol, atol=tol)
+        assert torch.allclose(host[pg, 1].view(kv, hd, page)[:, :vdim, off], v[t], rtol=tol, atol=tol)
+        if hd > dim:
+            assert float(host[pg, 0, :, off, dim:].abs().max()) == 0.0
+    untouched = [s for s in range(n_pages * page) if s not in set(int(x) for x in slots)]
+    pg, off = untouched[0] // page, untouched[0] % page
+    assert float(host[pg, 0, 0, off, 0]) == 7.0
+
+
+def _paged_case(dtype, n_heads, n_kv, hd, page_size, contexts, q_lens, seed, spikes=()):
+    """Queries and keys of unit root mean square in a paged cache with shuffled pages. ``spikes`` = (sequence, key
+    position): that key equals the sequence's last query's first head of each group."""
+    gen = torch.Generator().manual_seed(seed)
+    n_seqs, n_tok = len(contexts), sum(q_lens)
+    totals = [c + q for c, q in zip(contexts, q_lens)]
+    pages_of = [-(-t // page_size) for t in totals]
+    n_pages = sum(pages_of) + 3
+    order = torch.randperm(n_pages, generator=gen).tolist()
+    tables = torch.full((n_seqs, max(pages_of)), -1, dtype=torch.int32)
+    cache = torch.zeros((n_pages, 2, n_kv, page_size, hd))
+    unit = lambda x: x / x.pow(2).mean(-1, keepdim=True).sqrt()
+    q = unit(torch.randn(n_tok, n_heads, hd, generator=gen)).reshape(n_tok, n_heads * hd)
+    keys, values, group, row = [], [], n_heads // n_kv, 0
+    for s in range(n_seqs):
+        k = unit(torch.randn(totals[s], n_kv, hd, generator=gen))
+        v = torch.randn(totals[s], n_kv, hd, generator=gen)
+        last = row + q_lens[s] - 1
+        for seq, where in spikes:
+            if seq == s:
+                for g in range(n_kv):
+                    k[where, g] = q[last].view(n_heads, hd)[g * group]
+        keys.append(k)
+        values.append(v)
+        for lp in range(pages_of[s]):
+            page = order.pop()
+            tables[s, lp] = page
+            lo, hi = lp * page_size, min((lp + 1) * page_size, totals[s])
+            cache[page, 0, :, :hi - lo] = k[lo:hi].transpose(0, 1)
+            cache[page, 1].view(n_kv, hd, page_size)[:, :, :hi - lo] = v[lo:hi].permute(1, 2, 0)
+        row += q_lens[s]
+    tok_seq = torch.tensor([s for s in range(n_seqs) for _ in range(q_lens[s])], dtype=torch.int32)
+    positions = torch.tensor([contexts[s] + i for s in range(n_seqs) for i in range(q_lens[s])], dtype=torch.int32)
+    cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    meta = {"tables": tables.to(DEVICE), "tok_seq": tok_seq.to(DEVICE), "positions": positions.to(DEVICE),
+            "cu_q": cu_q.to(DEVICE), "contexts": torch.tensor(contexts, dtype=torch.int32, device=DEVICE)}
+    return q.to(dtype).to(DEVICE), cache.to(dtype).to(DEVICE), meta, keys, values
+
+
+def _plain_attend(q, keys, values, contexts, q_lens, n_heads, n_kv, hd, scale, rule, size, sink):
+    out = torch.zeros(q.shape[0], n_heads, hd, dtype=F64)
+    group, row = n_heads // n_kv, 0
+    for s, (c, n) in enumerate(zip(contexts, q_lens)):
+        k, v = keys[s].double(), values[s].double()
+        seen = plain.visible(c + n, rule, size)[c:]
+        qs = q[row:row + n].double().view(n, n_heads, hd)
+        kv_of = torch.arange(n_heads) // group
+        scores = torch.einsum("ihd,jhd->hij", qs, k[:, kv_of]) * scale
+        a = plain.attention_weights(scores, seen, sink)
+        out[row:row + n] = torch.einsum("hij,jhv->ihv", a, v[:, kv_of])
+        row += n
+    return out.view(q.shape[0], n_heads * hd)
+
+
+@pytest.mark.parametrize("kernel, dtype, hd, group", [
+    ("simt", torch.float32, 48, 3), ("simt", torch.float32, 128, 2), ("simt", torch.bfloat16, 32, 1),
+    ("simt", torch.float32, 64, 8), ("mma", torch.bfloat16, 64, 4), ("mma", torch.bfloat16, 128, 2),
+    ("mma", torch.bfloat16, 64, 1), ("mma", torch.bfloat16, 128, 8), ("tc", torch.bfloat16, 128, 2),
+    ("tc", torch.bfloat16, 128, 4), ("tc", torch.bfloat16, 128, 1)])
+@pytest.mark.parametrize("size", [44, 21, 16, 7, 64, 33, 150, 1, 128, 1000])
+def test_attention_kernels_over_blocks_of_positions(kernel, dtype, hd, group, size):
+    """Prompt portions and single tokens in one launch, shuffled pages, key splits, a sink of zero. The last query
+    of every sequence meets a key equal to itself at the first position of its own block and at the last position
+    of the block before: with a sharp scale each of them would take the softmax, and only the first may."""
+    n_kv, n_heads, page = 2, 2 * group, 16
+    contexts, q_lens = [70, 5, 300, 0, 131], [1, 37, 1, 45, 2]
+    if kernel == "tc":                     # prompt portions only
+        contexts, q_lens = [70, 5, 130, 600, 0], [40, 37, 64, 150, 300]
+    spikes = []
+    for s, (c, n) in enumerate(zip(contexts, q_lens)):
+        last = c + n - 1
+        start = last - last % size
+        spikes += [(s, j) for j in (start - 1, start) if 0 <= j < last]
+    q, cache, meta, keys, values = _paged_case(dtype, n_heads, n_kv, hd, page, contexts, q_lens, seed=hd + group + size,
+                                               spikes=spikes)
+    scale = 12.0 / hd                                       # a key equal to the query scores 12, the others about 0
+    n_tok = sum(q_lens)
+    sink = torch.zeros(n_heads, dtype=torch.float32, device=DEVICE)
+    status = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+    rounded_keys = [k.to(dtype).float() for k in keys]
+    rounded_values = [v.to(dtype).float() for v in values]
+    want = _plain_attend(q.cpu().float(), rounded_keys, rounded_values, contexts, q_lens, n_heads, n_kv, hd, scale,
+                         "chunk", size, sink.cpu())
+    for n_splits in (1, 3):
+        out = torch.zeros(n_tok, n_heads * hd, dtype=dtype, device=DEVICE)
+        scratch = None
+        if n_splits > 1:
+            scratch = torch.empty(kernels.attention_scratch_bytes(n_tok, n_heads, hd, n_splits) // 4 + 4,
+                                  dtype=torch.float32, device=DEVICE)
+        common = dict(n_splits=n_splits, scratch=scratch, sink=sink)
+        if kernel == "simt":
+            kernels.paged_attention(q, q.stride(0), cache, meta["tables"], meta["tok_seq"], meta["positions"], n_tok,
+                                    n_heads, n_kv, hd, -size, scale, out, status, **common)
+        elif kernel == "tc":
+            _, wide = kernels.attention_tile_lists([max(n, 17) for n in q_lens], group, True)
+            tiles = torch.tensor(wide, dtype=torch.int32, device=DEVICE)
+            kernels.paged_attention_tc(q, q.stride(0), cache, meta["tables"], meta["cu_q"], meta["contexts"], tiles,
+                                       len(wide) // 2, n_tok, n_heads, n_kv, hd, -size, scale, out, status, **common)
+        else:
+            narrow, wide = kernels.attention_tile_lists(q_lens, group, False)
+            if n_splits > 1:        # key splits need a launch that covers every token: all tiles wide
+                narrow, wide = [], [x for s, n in enumerate(q_lens) for r in range(0, n * group, 64) for x in (s, r)]
+            for tiles, is_narrow in ((narrow, True), (wide, False)):
+                if tiles:
+                    t = torch.tensor(tiles, dtype=torch.int32, device=DEVICE)
+                    kernels.paged_attention_mma(q, q.stride(0), cache, meta["tables"], meta["cu_q"], meta["contexts"], t,
+                                                len(tiles) // 2, is_narrow, n_tok, n_heads, n_kv, hd, -size, scale, out,
+                                                status, **common)
+        tol = 2e-5 if dtype == torch.float32 else 0.03
+        got = out.double().cpu()
+        assert torch.allclose(got, want, rtol=tol, atol=tol), (n_splits, (got - want).abs().max())
+        assert int(status.item()) == 0
+    # the planted keys matter: with blocks that start one position earlier, the last rows come out differently
+    if size > 1:
+        shifted = []
+        for s, (c, n) in enumerate(zip(contexts, q_lens)):
+            last = c + n - 1
+            if last - last % size - 1 >= 0:
+                shifted.append(s)
+        causal = _plain_attend(q.cpu().float(), rounded_keys, rounded_values, contexts, q_lens, n_heads, n_kv, hd,
+                               scale, "causal", 0, sink.cpu())
+        last_rows = [int(x) - 1 for x in np.cumsum(q_lens)]
+        moved = [float((causal[last_rows[s]] - want[last_rows[s]]).abs().max()) for s in shifted]
+        assert not moved or min(moved) > 0.05
+
+
+def _latent_case(dtype, heads, rank, rot, page_size, contexts, q_lens, seed, spikes=()):
+    gen = torch.Generator().manual_seed(seed)
+    dk = rank + rot
+    n_seqs, n_tok = len(contexts), sum(q_lens)
+    totals = [c + q for c, q in zip(contexts, q_lens)]
+    pages_of = [-(-t // page_size) for t in totals]
+    n_pages = sum(pages_of) + 2
+    order = torch.randperm(n_pages, generator=gen).tolist()
+    tables = torch.full((n_seqs, max(pages_of)), -1, dtype=torch.int32)
+    cache = torch.zeros((n_pages, 1, 1, page_size, dk))
+    unit = lambda x: x / x.pow(2).mean(-1, keepdim=True).sqrt()
+    q = unit(torch.randn(n_tok, heads, dk, generator=gen))
+    vectors, row = [], 0
+    for s in range(n_seqs):
+        c = unit(torch.randn(totals[s], dk, generator=gen))
+        last = row + q_lens[s] - 1
+        for seq, where in spikes:
+            if seq == s:
+                c[where] = q[last, 0]
+        vectors.append(c)
+        for lp in range(pages_of[s]):
+            page = order.pop()
+            tables[s, lp] = page
+            lo, hi = lp * page_size, min((lp + 1) * page_size, totals[s])
+            cache[page, 0, 0, :hi - lo] = c[lo:hi]
+        row += q_lens[s]
+    tok_seq = torch.tensor([s for s in range(n_seqs) for _ in range(q_lens[s])], dtype=torch.int32)
+    positions = torch.tensor([contexts[s] + i for s in range(n_seqs) for i in range(q_lens[s])], dtype=torch.int32)
+    cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    meta = {"tables": tables.to(DEVICE), "tok_seq": tok_seq.to(DEVICE), "positions": positions.to(DEVICE),
+            "cu_q": cu_q.to(DEVICE), "contexts": torch.tensor(contexts, dtype=torch.int32, device=DEVICE)}
+    return q.to(dtype).to(DEVICE), cache.to(dtype).to(DEVICE), meta, vectors
+
+
+@pytest.mark.parametrize("kernel, dtype, heads, rank, rot", [
+    ("simt", torch.float32, 3, 20, 6), ("simt", torch.float32, 9, 64, 16), ("simt", torch.bfloat16, 2, 40, 8),
+    ("mma", torch.bfloat16, 4, 64, 16), ("mma", torch.bfloat16, 5, 96, 32), ("mma", torch.bfloat16, 16, 128, 0)])
+@pytest.mark.parametrize("window", [9, 33, 130, 1, 1000])
+def test_latent_attention_kernels_with_a_sink_under_a_window(kernel, dtype, heads, rank, rot, window):
+    """The softmax's denominator holds exp(sink) of the head once, whatever the number of key splits; a key equal
+    to the last query sits just inside and just outside the window."""
+    contexts, q_lens = [70, 5, 300, 0, 131], [1, 37, 1, 45, 2]
+    spikes = []
+    for s, (c, n) in enumerate(zip(contexts, q_lens)):
+        last = c + n - 1
+        spikes += [(s, j) for j in (last - window, last - window + 1) if 0 <= j < last]
+    q, cache, meta, vectors = _latent_case(dtype, heads, rank, rot, 16, contexts, q_lens, seed=rank + window, spikes=spikes)
+    dk, n_tok = rank + rot, sum(q_lens)
+    scale = 10.0 / dk
+    sink = (torch.randn(heads, generator=torch.Generator().manual_seed(3)) * 2.0).float()
+    want = torch.zeros(n_tok, heads, rank, dtype=F64)
+    row = 0
+    for s, (c, n) in enumerate(zip(contexts, q_lens)):
+        vec = vectors[s].to(dtype).double()
+        qs = q[row:row + n].double().cpu()
+        scores = torch.einsum("ihd,jd->hij", qs, vec) * scale
+        a = plain.attention_weights(scores, plain.visible(c + n, "window", window)[c:], sink)
+        want[row:row + n] = torch.einsum("hij,jr->ihr", a, vec[:, :rank])
+        row += n
+    status = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+    tol = 2e-5 if dtype == torch.float32 else 0.03
+    for n_splits in (1, 3):
+        out = torch.zeros(n_tok, heads, rank, dtype=dtype, device=DEVICE)
+        if kernel == "simt":
+            if n_splits > 1:
+                continue
+            kernels.latent_attention(q, cache, meta["tables"], meta["tok_seq"], meta["positions"], rank, window, scale,
+                                     out, status, sink=sink.to(DEVICE))
+        else:
+            flat = kernels.latent_tile_list(q_lens, heads)
+            tiles = torch.tensor(flat, dtype=torch.int32, device=DEVICE)
+            scratch = None
+            if n_splits > 1:
+                scratch = torch.empty(kernels.attention_scratch_bytes(n_tok, heads, rank, n_splits) // 4 + 4,
+                                      dtype=torch.float32, device=DEVICE)
+            kernels.latent_attention_mma(q, cache, meta["tables"], meta["cu_q"], meta["contexts"], tiles, len(flat) // 2,
+                                         rank, window, scale, out, status, n_splits=n_splits, scratch=scratch,
+                                         sink=sink.to(DEVICE))
+        got = out.double().cpu()
+        assert torch.allclose(got, want, rtol=tol, atol=tol), (n_splits, (got - want).abs().max())
+        assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts, top", [(5, 2), (3, 1), (16, 2), (40, 5), (2, 2), (1, 1), (70, 8)])
+def test_router_kernel_takes_the_largest_logits_and_weighs_them_among_themselves(dtype, experts, top):
+    gen = torch.Generator().manual_seed(experts * 7 + top)
+    n, width = 50, 72
+    h = torch.randn(n, width, generator=gen).to(dtype)
+    router = torch.randn(experts, width, generator=gen) * 0.7
+    bias = torch.randn(experts, generator=gen) * 1.5
+    ids_out = torch.empty(n * top, dtype=torch.int32, device=DEVICE)
+    place = torch.empty(n * top, dtype=torch.int32, device=DEVICE)
+    counts = torch.zeros(experts, dtype=torch.int32, device=DEVICE)
+    weights = torch.empty(n * top, dtype=torch.float32, device=DEVICE)
+    kernels.moe_route_softmax(h.to(DEVICE), router.to(DEVICE), top, 0, None, ids_out, weights, counts, place,
+                              bias=bias.to(DEVICE))
+    chosen, want_weights, margin = plain.route(h.double(), router.double(), bias.double(), top)
+    got_ids = ids_out.view(n, top).cpu().long()
+    got_weights = weights.view(n, top).cpu().double()
+    clear = margin > 1e-3
+    assert torch.equal(torch.sort(got_ids[clear], dim=1).values, torch.sort(chosen[clear], dim=1).values)
+    # the bias decides some choices: without it others would win
+    without = plain.route(h.double(), router.double(), torch.zeros(experts, dtype=F64), top)[0]
+    assert experts == top or not torch.equal(torch.sort(without, 1).values, torch.sort(chosen, 1).values)
+    for t in range(n):
+        if not clear[t]:
+            continue
+        for slot in range(top):
+            where = (chosen[t] == got_ids[t, slot]).nonzero()[0, 0]
+            assert abs(float(got_weights[t, slot] - want_weights[t, where])) < 1e-5
+    assert int(counts.sum()) == n * top
+    assert torch.allclose(got_weights.sum(1), torch.ones(n, dtype=F64), atol=1e-5)
+
+
+# ---------------------------------------------------------------------- single layers
+LAYERS_ALONE = {
+    "blocks": (blocks(6, 3, 24, 40, 0.5, (12, 1000.0), 11), None),
+    "blocks_of_one_page_tensor_core_head": (blocks(4, 1, 64, 64, 0.25, (64, 10000.0), 16), None),
+    "blocks_head_128": (blocks(2, 2, 128, 128, 0.15, (32, 10000.0), 24), None),
+    "blocks_longer_than_the_prompt_no_rotation": (blocks(2, 1, 32, 16, 0.4, None, 500), None),
+    "capped": (capped(4, 1, 40, 8, 0.5, (40, 50000.0), 3.0), None),
+    "capped_tensor_core_head": (capped(4, 2, 64, 64, 0.3, (16, 10000.0), 2.0), None),
+    "latent": (latent(3, 24, 8, 20, 40, 32, 0.35, 300.0, 9), None),
+    "latent_many_heads": (latent(9, 16, 8, 8, 16, 24, 0.4, 1000.0, 40), None),
+    "latent_tensor_core_rank": (latent(4, 32, 16, 32, 48, 64, 0.25, 5000.0, 21), None),
+    "latent_without_rotated_part": (latent(2, 16, 0, 16, 20, 32, 0.4, 100.0, 30), None),
+    "dense_feed_forward": (blocks(2, 2, 16, 16, 0.4, (8, 100.0), 20, mlp=dense(72)), None),
+    "experts_top_two": (blocks(2, 2, 16, 16, 0.4, (8, 100.0), 20, mlp=moe(40, 5, 2)), None),
+    "experts_top_one": (capped(2, 2, 16, 16, 0.4, (8, 100.0), 5.0, mlp=moe(24, 3, 1)), None),
+    "all_experts_chosen": (latent(2, 16, 4, 16, 16, 16, 0.4, 100.0, 30, mlp=moe(32, 3, 3)), None),
+    "repeated_three_times": (blocks(2, 2, 16, 16, 0.4, (8, 100.0), 13, mlp=dense(40)), (0, 1, 3)),
+    "repeated_once": (latent(2, 16, 4, 16, 16, 16, 0.4, 100.0, 30, mlp=moe(32, 4, 2)), (0, 1, 1)),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(LAYERS_ALONE))
+def test_one_layer_models(name, dtype):
+    """Whole, then one token at a time, then in portions: the three must agree with the plain model."""
+    layer, loop = LAYERS_ALONE[name]
+    raw = single_layer(layer, width=64, vocab=120, loop=loop)
+    tensors = draw(raw, seed=len(name), router_gain=3.0)
+    run = Run(raw, tensors, dtype, max_tokens=4 * 256)
+    tokens = ids(75, raw["vocab"], seed=1)
+    run.feed("whole", tokens, [75])
+    run.check("whole", tokens)
+    run.feed("single", tokens[:60], [])
+    run.check("single", tokens[:60])
+    run.feed("cut", tokens, cycle)
+    run.check("cut", tokens)
+
+
+def _planted(layer, seed=9):
+    """A one-layer model without rotation whose last token's query is aligned with the key of one token that occurs
+    nowhere else: where that token stands decides the last logits if and only if the last query sees it."""
+    raw = single_layer(layer, width=64, vocab=90)
+    tensors = draw(raw, seed=seed)
+    return raw, tensors
+
+
+def _aligned_grouped(raw, tensors):
+    """q of token 89 = key direction of token 88, for every head (the norms keep directions)."""
+    eps = raw["norm"]["eps"]
+    m = raw["layers"][0]["mixer"]
+    norm1 = tensors["l0.norm1"]
+    h88 = plain.rms_norm(tensors["embed"][88], norm1, eps)
+    h89 = plain.rms_norm(tensors["embed"][89], norm1, eps)
+    k88 = (tensors["l0.mix.k"] @ h88).view(m["kv_heads"], m["dim"])
+    group = m["heads"] // m["kv_heads"]
+    target = torch.cat([k88[h // group] for h in range(m["heads"])])
+    tensors["l0.mix.q"] = (torch.outer(target, h89) / (h89 @ h89)).contiguous()
+    tensors["l0.mix.q.norm"] = torch.ones(m["dim"])
+    tensors["l0.mix.k.norm"] = torch.ones(m["dim"])
+
+
+def _aligned_latent(raw, tensors):
+    """Token 89's query latent expands to the plain key of token 88 in every head; no rotated part to blur it."""
+    eps = raw["norm"]["eps"]
+    m = raw["layers"][0]["mixer"]
+    norm1 = tensors["l0.norm1"]
+    h88 = plain.rms_norm(tensors["embed"][88], norm1, eps)
+    h89 = plain.rms_norm(tensors["embed"][89], norm1, eps)
+    down = tensors["l0.mix.dkv"] @ h88
+    c88 = plain.rms_norm(down[:m["kv_rank"]], tensors["l0.mix.dkv.norm"], eps)
+    k88 = tensors["l0.mix.uk"] @ c88                                        # [heads * dim]
+    cq89 = plain.rms_norm(tensors["l0.mix.dq"] @ h89, tensors["l0.mix.dq.norm"], eps)
+    uq = torch.zeros(m["heads"], m["dim"] + m["rot_dim"], m["q_rank"])
+    uq[:, :m["dim"], :] = torch.einsum("hd,r->hdr", k88.view(m["heads"], m["dim"]), cq89 / (cq89 @ cq89)) * 3.0
+    tensors["l0.mix.uq"] = uq.reshape(-1, m["q_rank"]).contiguous()
+
+
+PLANTED = {
+    # (layer, how to align, rule, size, length)
+    "blocks_of_45": (blocks(2, 1, 32, 32, 0.6, None, 45), _aligned_grouped, "chunk", 45, 180),
+    "blocks_of_16": (blocks(2, 2, 32, 48, 0.6, None, 16), _aligned_grouped, "chunk", 16, 100),
+    "blocks_of_200": (blocks(4, 2, 64, 64, 0.5, None, 200), _aligned_grouped, "chunk", 200, 430),
+    "everything_in_sight": (capped(2, 1, 32, 32, 0.6, None, 40.0), _aligned_grouped, "causal", 0, 430),
+    "window_of_33": (latent(2, 32, 4, 32, 24, 32, 0.5, 100.0, 33), _aligned_latent, "window", 33, 430),
+    "window_of_64": (latent(3, 16, 0, 16, 16, 64, 0.7, 100.0, 64), _aligned_latent, "window", 64, 200),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("decode", [0, 50])
+@pytest.mark.parametrize("name", list(PLANTED))
+def test_a_token_decides_exactly_where_the_last_query_sees_it(name, decode, dtype):
+    """The asked-for token far back, at both edges of the last query's block or window and at page borders, in a
+    whole prompt and with the tail decoded token by token across page, block and window borders."""
+    layer, align, rule, size, length = PLANTED[name]
+    raw, tensors = _planted(layer)
+    align(raw, tensors)
+    tokens = [t % 86 for t in ids(length, 86, seed=2)]
+    tokens[-1] = 89
+    run = Run(raw, tensors, dtype, max_tokens=2 * (length + 64))
+    last = length - 1
+    if rule == "chunk":
+        edge = last - last % size
+    elif rule == "window":
+        edge = last - size + 1
+    else:
+        edge = 0
+    places = {0, 1, 15, 16, 17, edge - 20, edge - 2, edge - 1, edge, edge + 1, last - 1}
+    seen = plain.visible(length, rule, size)[last]
+    base = None
+    for turn, place in enumerate([None] + sorted(p for p in places if 0 <= p < last)):
+        planted = list(tokens)
+        if place is not None:
+            planted[place] = 88
+        request = f"p{turn}"
+        run.feed(request, planted, [length - decode] if decode else [length])
+        run.check(request, planted)
+        row = run.logits[(request, last)]
+        if place is None:
+            base = row
+            continue
+        moved = float(np.abs(row - base).max())
+        if bool(seen[place]):
+            assert moved > 0.3, (place, moved)
+        else:
+            assert moved <= (1e-4 if dtype == "float32" else 0.03), (place, moved)
+
+
+# ---------------------------------------------------------------------- whole models
+@pytest.fixture(scope="module", params=[(n, d) for n in ("A", "B", "C", "D") for d in ("float32", "bfloat16")],
+                ids=lambda p: f"{p[0]}-{p[1]}")
+def run(request):
+    name, dtype = request.param
+    raw = MODELS[name]
+    # four live requests of at most 128 tokens: pages and slots must come back to be used again
+    made = Run(raw, draw(raw, seed=11 + ord(name), router_gain=2.0), dtype, max_tokens=4 * 128, max_requests=4)
+    yield made
+
+
+LENGTHS = [1, 2, 17, 40, 65, 100, 128]
+
+
+def prompts_of(run):
+    return {f"r{n}": ids(n, run.raw["vocab"], seed=100 + n) for n in LENGTHS}
+
+
+def test_whole_prompts(run):
+    for request, tokens in prompts_of(run).items():
+        run.feed(request + "w", tokens, [len(tokens)])
+        run.check(request + "w", tokens)
+
+
+def test_prefill_then_token_by_token(run):
+    for request, tokens in prompts_of(run).items():
+        head = max(len(tokens) - 70, 0)
+        run.feed(request + "d", tokens, [head] if head else [])
+        run.check(request + "d", tokens)
+
+
+def test_portions_down_to_two_tokens(run):
+    for shift, (request, tokens) in enumerate(prompts_of(run).items()):
+        run.feed(request + "c", tokens, lambda turn: cycle(turn + shift))
+        run.check(request + "c", tokens)
+    tokens = prompts_of(run)["r65"]
+    run.feed("pairs", tokens, lambda turn: 2)
+    run.check("pairs", tokens)
+
+
+def test_unequal_requests_batched_with_pages_and_slots_used_again(run):
+    prompts = prompts_of(run)
+    waiting = [(f"{request}m{again}", tokens) for again in range(2) for request, tokens in prompts.items()]
+    tokens_of = dict(waiting)
+    live: dict[str, int] = {}
+    cache = run.replayer.core.cache
+    turn = 0
+    while waiting or live:
+        while waiting and len(live) < 4:
+            live[waiting.pop(0)[0]] = 0
+        portions, ended = [], []
+        for place, (request, done) in enumerate(list(live.items())):
+            tokens = tokens_of[request]
+            if (turn + place) % 5 == 4 and len(live) > 1:
+                continue                                          # sits this step out
+            remaining = len(tokens) - done
+            size = 1 if (turn + place) % 3 == 0 else min(cycle(turn + place), remaining)
+            portions.append((request, tokens[done:done + size]))
+            live[request] = done + size
+            if done + size == len(tokens):
+                ended.append(request)
+        turn += 1
+        if portions:
+            run.step(portions, end=ended)
+        for request in ended:
+            del live[request]
+    for request, tokens in tokens_of.items():
+        run.check(request, tokens)
+    assert cache.pages_reused > 0
+    assert len(set(run.slots_seen[r] for r in tokens_of)) <= 4 < len(tokens_of)
+
+
+def test_long_decoding(run):
+    """Hundreds of single-token steps (the captured decode step replayed) after a short prompt, two requests
+    side by side, one of them starting later: every block border and window passes over decoded tokens many times."""
+    a = ids(260, run.raw["vocab"], seed=7)
+    b = ids(150, run.raw["vocab"], seed=8)
+    run.step([("la", a[:6])])
+    for i in range(6, len(a)):
+        portions = [("la", a[i:i + 1])]
+        j = i - 100
+        if 0 <= j < len(b):
+            portions.append(("lb", b[j:j + 1]))
+        ended = [name for name, k, seq in (("la", i, a), ("lb", j, b)) if k == len(seq) - 1]
+        run.step(portions, end=ended)
+    run.check("la", a)
+    run.check("lb", b)
+
+
+def test_routing_was_mostly_clear():
+    assert Run.clear >= 2 * Run.unclear, "most choices must have been clear enough to be compared"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompts(dtype):
+    """A prompt long enough for the prompt-sized product kernels and many attention tiles, blocks and windows of
+    many key chunks: whole, then in uneven portions with the tail decoded."""
+    raw, length = MODELS["L"], 1100
+    run = Run(raw, draw(raw, seed=21, router_gain=2.0), dtype, max_tokens=2 * (length + 64))
+    tokens = ids(length, raw["vocab"], seed=5)
+    run.feed("whole", tokens, [length])
+    run.check("whole", tokens)
+    run.feed("cut", tokens, [length // 3 + 1, 2, length // 2, length - 40 - (length // 3 + 3 + length // 2)])
+    run.check("cut", tokens)
+
+
+def test_greedy_generation_through_the_engine_entry_point():
+    from matricxon_b200 import ChatEngine, GenerationRequest, SamplingConfig
+
+    raw = MODELS["A"]
+    tensors = draw(raw, seed=11)
+    config = config_from_dict(copy.deepcopy(raw))
+    model = model_from_tensors(config, tensors, dtype="float32", device=DEVICE)
+    engine = ChatEngine(model, max_cache_tokens=4 * 128, max_active=3, max_batched_tokens=64, prefill_chunk=24,
+                        max_model_len=128)
+    prompts = [ids(n, raw["vocab"], seed=40 + n) for n in (5, 33, 70, 12, 50)]
+    sampling = SamplingConfig(temperature=0.0, repeat_penalty=1.0, num_predict=24, num_ctx=128, seed=0)
+    results = engine.generate_batch([GenerationRequest(input_ids=p, sampling=sampling) for p in prompts])
+    weights = doubles(tensors)
+    for prompt, result in zip(prompts, results):
+        assert result.finish_reason == "length" and len(result.token_ids) == 24
+        logits = plain.forward(raw, weights, prompt + result.token_ids[:-1]).numpy()
+        for k, token in enumerate(result.token_ids):
+            row = logits[len(prompt) - 1 + k]
+            assert row[token] >= row.max() - 2e-3, (k, token, int(row.argmax()))
+
+
+def test_trace_program_and_command_line(tmp_path):
+    """The replay program itself on a model folder (bfloat16 file, both dtypes), and the generation command."""
+    from matricxon_b200.weights.safetensors_io import write_safetensors
+
+    raw = copy.deepcopy(MODELS["C"])
+    tensors = draw(raw, seed=12, store_dtype=torch.bfloat16, router_gain=3.0)
+    folder = tmp_path / "model"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(raw))
+    write_safetensors(folder / "model.safetensors", tensors.items())
+    tokens = ids(50, raw["vocab"], seed=3)
+    want = plain.forward(raw, {k: v.double() for k, v in tensors.items()}, tokens).numpy()
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:31], "want": [0, 30]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": tokens[31:33], "want": []},
+                                     {"id": "b", "tokens": tokens[:9], "want": [8]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": tokens[33:], "want": [16]}], "end": ["a"]}]
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / dtype
+        done = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype",
+                               dtype, "--out", str(out), "--max-tokens", "128"],
+                              input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                              timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
+        assert [line for line in done.stdout.splitlines() if line.startswith("done")] == ["done 0", "done 1", "done 2"]
+        got = {s: np.fromfile(out / f"{s}.f32", dtype="<f4").reshape(-1, raw["vocab"]) for s in (0, 1, 2)}
+        limit = limit_for(dtype, want) * (1 if dtype == "float32" else 2)
+        assert np.abs(got[0] - want[[0, 30]]).max() <= limit
+        assert np.abs(got[1] - want[[8]]).max() <= limit
+        assert np.abs(got[2] - want[[49]]).max() <= limit
+    config_path = tmp_path / "config.json"
+    config_path.write_text(json.dumps(MODELS["B"]))
+    done = subprocess.run([sys.executable, "-m", "matricxon_b200.generate", "--random-config", str(config_path),
+                           "--prompt-len", "20", "--num-predict", "12"], capture_output=True, text=True,
+                          timeout=600, cwd=str(ROOT))
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert "finish_reason:  length" in done.stdout and "Kefasun" in done.stdout
