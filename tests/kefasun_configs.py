@@ -64,10 +64,10 @@ MODEL_A = model(96, 211, 0.6, [
 # four, two and one query heads, a block of one page, a run of one layer repeated twice in the middle, a logit
 # scale of one, the capped kind first and the block-masked kind last
 MODEL_B = model(128, 257, 1.0, [
-    capped(8, 2, 64, 64, 0.25, (64, 10000.0), 30.0, mlp=moe(96, 4, 2)),
-    blocks(4, 2, 128, 128, 0.15, (32, 700.0), 16, mlp=None),
-    latent(4, 32, 16, 32, 64, 64, 0.25, 5000.0, 40, mlp=dense(160)),
-    blocks(2, 2, 64, 128, 0.25, (16, 10000.0), 50, mlp=moe(64, 9, 3)),
+    capped(8, 2, 64, 64, 0.15, (64, 10000.0), 30.0, mlp=moe(96, 4, 2)),
+    blocks(4, 2, 128, 128, 0.1, (32, 700.0), 16, mlp=None),
+    latent(4, 32, 16, 32, 64, 64, 0.2, 5000.0, 40, mlp=dense(160)),
+    blocks(2, 2, 64, 128, 0.15, (16, 10000.0), 50, mlp=moe(64, 9, 3)),
 ], loop=(1, 2, 2))
 
 # sizes that are multiples of nothing useful: width 100, odd vocabulary, heads of 12 and 20, six rotated entries,
@@ -86,10 +86,10 @@ MODEL_D = model(64, 97, 1.5, [
 # a middle size for long prompts: products of more than a thousand rows, blocks and windows of many key chunks, heads
 # of 64 in a group of four and of 128 in a group of two
 MODEL_L = model(256, 512, 0.5, [
-    blocks(8, 2, 64, 64, 0.25, (64, 10000.0), 300, mlp=moe(128, 8, 2)),
-    latent(4, 64, 32, 64, 96, 128, 0.18, 10000.0, 200, mlp=moe(64, 6, 3)),
-    capped(4, 2, 128, 128, 0.15, (128, 500000.0), 20.0, mlp=dense(384)),
-    blocks(4, 2, 128, 128, 0.15, (64, 10000.0), 130, mlp=None),
+    blocks(8, 2, 64, 64, 0.15, (64, 10000.0), 300, mlp=moe(128, 8, 2)),
+    latent(4, 64, 32, 64, 96, 128, 0.12, 10000.0, 200, mlp=moe(64, 6, 3)),
+    capped(4, 2, 128, 128, 0.1, (128, 500000.0), 20.0, mlp=dense(384)),
+    blocks(4, 2, 128, 128, 0.1, (64, 10000.0), 130, mlp=None),
 ], loop=(1, 3, 2))
 
 MODELS = {"A": MODEL_A, "B": MODEL_B, "C": MODEL_C, "D": MODEL_D, "L": MODEL_L}
