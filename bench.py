@@ -19,6 +19,8 @@ step and in 512-token steps, decode steps at several batch sizes; random weights
 models (mixed attention and recurrent layers, gated feed-forwards, a float residual stream).
 ``--compare bafusun`` does the same for the Bafusun architecture beside Parunex, the closest of the engine's other
 models (rotated windowed attention, routed experts through the same grouped products, a float residual stream).
+``--compare kefasun`` does the same for the Kefasun architecture beside Bafusun, the closest of the engine's other
+models (attention in every layer with normalised queries and keys, routed experts, norms on the branches).
 """
 
 from __future__ import annotations
@@ -399,6 +401,30 @@ def bafusun_config(size: dict) -> dict:
             "logit_scale": 1.0, "norm": {"eps": 1e-5}, "token_side": {"dim": BAFUSUN_SIDE_DIM}, "layers": layers}
 
 
+def kefasun_config(size: dict) -> dict:
+    """Six layers of which the second and third run twice (eight layer runs): block-masked attention, latent
+    attention and capped attention with 128-wide heads over 4 KV heads (latent sizes as Busatar's at the same width,
+    queries through a latent of three times the key/value rank), blocks and windows of 4,096 positions; the first
+    layer with a dense gated feed-forward, the others with eight experts of half that width, two per token."""
+    w, h = size["width"], size["width"] // 128
+    dense = {"kind": "dense", "ff": size["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": size["ff"] // 2}, "router": {"experts": 8, "top": 2}}
+    blocks = {"type": "attention",
+              "mixer": {"heads": h, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                        "rot": {"base": 1000000.0, "dims": 64}, "mask": {"size": COMPARE_WINDOW}}}
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": size["heads"], "dim": size["dim"], "rot_dim": size["rot"], "vdim": size["dim"],
+                        "q_rank": 3 * size["rank"], "kv_rank": size["rank"], "scale": (size["dim"] + size["rot"]) ** -0.5,
+                        "rot": {"base": 10000.0, "dims": size["rot"]}, "mask": {"size": COMPARE_WINDOW}}}
+    capped = {"type": "attention_2",
+              "mixer": {"heads": h, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+                        "rot": {"base": 1000000.0, "dims": 128}}}
+    order = [blocks, latent, capped, latent, blocks, latent]
+    layers = [dict(layer, mlp=dense if i == 0 else routed) for i, layer in enumerate(order)]
+    return {"architecture": "Kefasun", "vocab": COMPARE_VOCAB, "width": w, "logit_scale": 1.0, "norm": {"eps": 1e-5},
+            "loop": {"start": 1, "stop": 3, "times": 2}, "layers": layers}
+
+
 def starcoder2_like(size: dict) -> dict:
     return dict(STARCODER2_3B, num_hidden_layers=COMPARE_LAYERS, hidden_size=size["width"],
                 num_attention_heads=size["width"] // 128, num_key_value_heads=4, head_dim=128,
@@ -496,7 +522,9 @@ def compare_designs(args) -> int:
     clocks.start()
     sizes = [s for s in args.compare_sizes.split(",") if s]
     batches = [int(b) for b in args.compare_batches.split(",")]
-    if args.compare == "bafusun":
+    if args.compare == "kefasun":
+        designs = (("kefasun", kefasun_config), ("bafusun", bafusun_config))
+    elif args.compare == "bafusun":
         designs = (("bafusun", bafusun_config), ("parunex", parunex_config))
     elif args.compare == "parunex":
         designs = (("parunex", parunex_config), ("busatar", busatar_config))
@@ -539,9 +567,10 @@ def main() -> int:
                         help="leave out the 7B and 15B workloads through the scheduler")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch every kernel of a decode step by itself (for profilers)")
-    parser.add_argument("--compare", choices=["busatar", "parunex", "bafusun"], default=None,
-                        help="instead of the headline workload: Busatar beside StarCoder2, Parunex beside Busatar, or "
-                             "Bafusun beside Parunex, at equal layer sizes (prefill and decode throughput at a few sizes)")
+    parser.add_argument("--compare", choices=["busatar", "parunex", "bafusun", "kefasun"], default=None,
+                        help="instead of the headline workload: Busatar beside StarCoder2, Parunex beside Busatar, "
+                             "Bafusun beside Parunex, or Kefasun beside Bafusun, at equal layer sizes (prefill and "
+                             "decode throughput at a few sizes)")
     parser.add_argument("--compare-only", default=None,
                         help="with --compare: measure only this one of the two designs (for profilers)")
     parser.add_argument("--compare-sizes", default="w1024,w2048")
