@@ -444,7 +444,9 @@ int launch_merge(const float* part_o, const float* part_ml, T* out, int out_stri
                           part_ml, out, out_stride, n_heads, head_dim, n_splits, (int)pairs, sink);
         return mx_launch_status();
     }
-    mx_launch_chained(attention_merge_kernel<T>, dim3(n_tokens, n_heads), dim3(128), 0, stream, part_o, part_ml, out,
+    // a thread per value column where the head allows (a latent of 512 columns took four passes with 128 threads)
+    const int threads = head_dim <= 128 ? 128 : (head_dim <= 256 ? 256 : 512);
+    mx_launch_chained(attention_merge_kernel<T>, dim3(n_tokens, n_heads), dim3(threads), 0, stream, part_o, part_ml, out,
                       out_stride, n_heads, head_dim, n_splits, sink);
     return mx_launch_status();
 }

@@ -23,6 +23,17 @@ namespace {
 
 constexpr int RMS_MAX_PER_THREAD = 16;   // row values a thread keeps in registers
 
+__device__ __forceinline__ void store4(float* dst, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 packed;
+    packed.x = *reinterpret_cast<unsigned*>(&lo);
+    packed.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = packed;
+}
+
 template <typename TOut>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                const float* __restrict__ weight, float offset, TOut* __restrict__ out,
@@ -158,6 +169,110 @@ __global__ void rmsnorm_branch_add_kernel(float* x, const float* y, const float*
         o[i] = from_float<TAct>((n < RMS_MAX_PER_THREAD ? kept[n] : xr[i]) * inv_x * wn[i]);
 }
 
+// The float4 forms of the two kernels above, for rows whose length (and stride) is a multiple of 4 and that fit in
+// RMS_VEC float4 a thread: one trip to memory for the row, which stays in registers between the passes. Few rows
+// (a decode step) get a thread per float4, so that the row's latency is all there is.
+template <typename TOut>
+__global__ void rmsnorm_vec_kernel(const float* x, const int* __restrict__ rows, const float* __restrict__ weight,
+                                   float offset, TOut* __restrict__ out, int hidden, float eps, long long x_stride) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    const int r = blockIdx.x;
+    const int vecs = hidden >> 2;
+    const float4* wr = reinterpret_cast<const float4*>(weight);
+    float4 w[RMS_VEC];
+#pragma unroll
+    for (int n = 0; n < RMS_VEC; ++n) {                       // the weight does not depend on the kernel before
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < vecs) w[n] = wr[i];
+    }
+    pdl_wait();
+    const float4* xr = reinterpret_cast<const float4*>(after_wait(x) + (size_t)(rows ? rows[r] : r) * x_stride);
+    float4 kept[RMS_VEC];
+    float s = 0.f;
+#pragma unroll
+    for (int n = 0; n < RMS_VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < vecs) {
+            kept[n] = xr[i];
+            s = fmaf(kept[n].x, kept[n].x, s); s = fmaf(kept[n].y, kept[n].y, s);
+            s = fmaf(kept[n].z, kept[n].z, s); s = fmaf(kept[n].w, kept[n].w, s);
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + eps);
+#pragma unroll
+    for (int n = 0; n < RMS_VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < vecs) {
+            TOut* dst = out + (size_t)r * hidden + 4 * i;
+            store4(dst, kept[n].x * inv * (offset + w[n].x), kept[n].y * inv * (offset + w[n].y),
+                   kept[n].z * inv * (offset + w[n].z), kept[n].w * inv * (offset + w[n].w));
+        }
+    }
+}
+
+template <typename TAct>
+__global__ void rmsnorm_branch_add_vec_kernel(float* x, const float* y, const float* __restrict__ wb,
+                                              const float* __restrict__ wn, TAct* out, int hidden, float eps) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    x = after_wait(x);
+    y = after_wait(y);
+    const int r = blockIdx.x;
+    const int vecs = hidden >> 2;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)r * hidden);
+    const float4* yr = reinterpret_cast<const float4*>(y + (size_t)r * hidden);
+    float4 branch[RMS_VEC], row[RMS_VEC];
+    float s = 0.f;
+#pragma unroll
+    for (int n = 0; n < RMS_VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < vecs) {
+            branch[n] = yr[i];
+            row[n] = xr[i];
+            s = fmaf(branch[n].x, branch[n].x, s); s = fmaf(branch[n].y, branch[n].y, s);
+            s = fmaf(branch[n].z, branch[n].z, s); s = fmaf(branch[n].w, branch[n].w, s);
+        }
+    }
+    const float inv_y = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + eps);
+    s = 0.f;
+#pragma unroll
+    for (int n = 0; n < RMS_VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < vecs) {
+            const float4 w = reinterpret_cast<const float4*>(wb)[i];
+            row[n] = make_float4(row[n].x + branch[n].x * inv_y * w.x, row[n].y + branch[n].y * inv_y * w.y,
+                                 row[n].z + branch[n].z * inv_y * w.z, row[n].w + branch[n].w * inv_y * w.w);
+            xr[i] = row[n];
+            s = fmaf(row[n].x, row[n].x, s); s = fmaf(row[n].y, row[n].y, s);
+            s = fmaf(row[n].z, row[n].z, s); s = fmaf(row[n].w, row[n].w, s);
+        }
+    }
+    if (out == nullptr) return;
+    float inv_x = 1.f;
+    if (wn != nullptr) inv_x = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + eps);
+#pragma unroll
+    for (int n = 0; n < RMS_VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < vecs) {
+            float4 w = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (wn != nullptr) w = reinterpret_cast<const float4*>(wn)[i];
+            store4(out + (size_t)r * hidden + 4 * i, row[n].x * inv_x * w.x, row[n].y * inv_x * w.y,
+                   row[n].z * inv_x * w.z, row[n].w * inv_x * w.w);
+        }
+    }
+}
+
+// Threads a row for the float4 kernels, or 0 when the row does not fit: a thread per float4 for few rows.
+int vec_threads_for(int n_rows, int hidden) {
+    if (hidden % 4 != 0) return 0;
+    const int vecs = hidden / 4;
+    int threads = n_rows <= 64 ? (vecs + 31) / 32 * 32 : (vecs >= 1024 ? 512 : 256);
+    threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+    return (long long)threads * RMS_VEC >= vecs ? threads : 0;
+}
+
 __global__ void cast_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long long count) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < count) out[i] = __float2bfloat16_rn(x[i]);
@@ -171,6 +286,16 @@ extern "C" int mx_rmsnorm(const float* x, const int* rows, const float* weight, 
                           int out_dtype, int n_rows, int hidden, float eps, long long x_stride, cudaStream_t stream) {
     if (n_rows <= 0) return MX_OK;
     if (hidden <= 0) MX_REFUSE("rmsnorm: hidden must be positive, got %d", hidden);
+    const int vec_threads = (x_stride % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0) ? vec_threads_for(n_rows, hidden) : 0;
+    if (vec_threads > 0) {
+        if (out_dtype == MX_DTYPE_F32)
+            mx_launch_chained(rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(vec_threads), 0, stream, x, rows, weight,
+                              offset, (float*)out, hidden, eps, x_stride);
+        else
+            mx_launch_chained(rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(vec_threads), 0, stream, x, rows,
+                              weight, offset, (__nv_bfloat16*)out, hidden, eps, x_stride);
+        return mx_launch_status();
+    }
     const int threads = threads_for(hidden);
     if (out_dtype == MX_DTYPE_F32)
         rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, rows, weight, offset, (float*)out, hidden, eps, x_stride);
@@ -184,6 +309,16 @@ extern "C" int mx_rmsnorm_branch_add(float* x, const float* y, const float* wb, 
                                      int out_dtype, int n_rows, int hidden, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return MX_OK;
     if (hidden <= 0) MX_REFUSE("rmsnorm: hidden must be positive, got %d", hidden);
+    const int vec_threads = vec_threads_for(n_rows, hidden);
+    if (vec_threads > 0) {
+        if (out_dtype == MX_DTYPE_F32)
+            mx_launch_chained(rmsnorm_branch_add_vec_kernel<float>, dim3(n_rows), dim3(vec_threads), 0, stream, x, y, wb,
+                              wn, (float*)out, hidden, eps);
+        else
+            mx_launch_chained(rmsnorm_branch_add_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(vec_threads), 0, stream, x,
+                              y, wb, wn, (__nv_bfloat16*)out, hidden, eps);
+        return mx_launch_status();
+    }
     // few rows (a decode step): the row's latency is all there is, so more threads a row
     const int threads = n_rows <= 64 ? min(1024, max(128, (hidden + 127) / 128 * 32)) : threads_for(hidden);
     if (out_dtype == MX_DTYPE_F32)
