@@ -555,7 +555,7 @@ PLANTED = {
     # (layer, how to align, rule, size, length)
     "blocks_of_45": (blocks(2, 1, 32, 32, 0.6, None, 45), _aligned_grouped, "chunk", 45, 180),
     "blocks_of_16": (blocks(2, 2, 32, 48, 0.6, None, 16), _aligned_grouped, "chunk", 16, 100),
-    "blocks_of_200": (blocks(4, 2, 64, 64, 0.5, None, 200), _aligned_grouped, "chunk", 200, 430),
+    "blocks_of_180": (blocks(4, 2, 64, 64, 0.5, None, 180), _aligned_grouped, "chunk", 180, 430),
     "everything_in_sight": (capped(2, 1, 32, 32, 0.6, None, 40.0), _aligned_grouped, "causal", 0, 430),
     "window_of_33": (latent(2, 32, 4, 32, 24, 32, 0.5, 100.0, 33), _aligned_latent, "window", 33, 430),
     "window_of_64": (latent(3, 16, 0, 16, 16, 64, 0.7, 100.0, 64), _aligned_latent, "window", 64, 200),
