@@ -9,7 +9,8 @@
 //   n(x) = x / sqrt(mean over the head's `dim` entries of x^2 + eps) * w, with one weight vector for all query heads
 //   and one for all key heads (null: the head is left as it is). The rotation comes after the norm and pairs entry
 //   i with entry i + rot/2 or, `interleaved`, entry 2i with entry 2i + 1 (i < rot/2):
-//   (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = position * freq[i] in float.
+//   (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = position * freq[i] in float; a token's cosines and sines
+//   are formed once per block, in shared memory.
 //   A warp owns a head (up to 256 entries in registers); blockIdx.y shares a token's heads out between blocks when
 //   tokens are few.
 #include <math.h>
@@ -27,11 +28,15 @@ norm_rotate_kv_write_kernel(const float* __restrict__ proj, int ld, const int* _
                             const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
                             const int* __restrict__ slots, T* __restrict__ cache, long long n_slots, int page_size,
                             T* __restrict__ q_out, int n_heads, int n_kv_heads, int dim, int vdim, int hd, int* status) {
+    extern __shared__ float cs[];                           // cos[half], sin[half] of the token's angles
     pdl_trigger();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float pos = (float)positions[t];                  // step metadata and constants: no kernel writes them
     const int half = rot >> 1;
+    // every head of the token turns by the same angles: once per block, not once per entry
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * freq[i], &cs[half + i], &cs[i]);
+    __syncthreads();
     long long slot = slots ? slots[t] : -1;
     if (slot != -1 && (slot < 0 || slot >= n_slots)) {
         if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, MX_STATUS_BAD_SLOT);
@@ -69,8 +74,7 @@ norm_rotate_kv_write_kernel(const float* __restrict__ proj, int ld, const int* _
                 const bool first = interleaved ? !(d & 1) : d < half;
                 const int other = interleaved ? d ^ 1 : (first ? d + half : d - half);
                 const float u = weight ? src[other] * inv * weight[other] : src[other];
-                float s, c;
-                sincosf(pos * freq[i], &s, &c);
+                const float c = cs[i], s = cs[half + i];
                 v = first ? v * c - u * s : v * c + u * s;
             }
             dst[d] = from_float<T>(v);
@@ -100,12 +104,13 @@ extern "C" int mx_norm_rotate_kv_write(const float* proj, int ld, const int* pos
     const long long n_slots = n_pages * page_size;
     const int pieces = n_tokens >= 512 ? 1 : max(1, min(32, (n_heads + n_kv_heads + NR_WARPS - 1) / NR_WARPS));
     const dim3 grid(n_tokens, pieces);
+    const size_t smem = (size_t)(rot > 0 ? rot : 1) * sizeof(float);
     if (dtype == MX_DTYPE_F32)
-        mx_launch_chained(norm_rotate_kv_write_kernel<float>, grid, dim3(NR_THREADS), 0, stream,
+        mx_launch_chained(norm_rotate_kv_write_kernel<float>, grid, dim3(NR_THREADS), smem, stream,
             proj, ld, positions, freq, rot, interleaved, q_weight, k_weight, eps, cache ? slots : nullptr, (float*)cache,
             n_slots, page_size, (float*)q_out, n_heads, n_kv_heads, dim, vdim, hd, status);
     else
-        mx_launch_chained(norm_rotate_kv_write_kernel<__nv_bfloat16>, grid, dim3(NR_THREADS), 0, stream,
+        mx_launch_chained(norm_rotate_kv_write_kernel<__nv_bfloat16>, grid, dim3(NR_THREADS), smem, stream,
             proj, ld, positions, freq, rot, interleaved, q_weight, k_weight, eps, cache ? slots : nullptr,
             (__nv_bfloat16*)cache, n_slots, page_size, (__nv_bfloat16*)q_out, n_heads, n_kv_heads, dim, vdim, hd, status);
     return mx_launch_status();
