@@ -15,6 +15,9 @@ caches of different kinds by layer index (app/runtime/mamba_cache.py:21-70). Her
   so no later query can see that page; its table entry becomes -1. A group whose
   windows keep the first ``keep_first`` positions in sight never gives back the pages
   that hold them;
+* a group whose queries see their own block of B positions only (blocks counted from the sequence's start) gives
+  a page back as soon as it lies wholly before the block of position ``length``: every later query sits in that
+  block or a later one;
 * a finished request gives everything back; freed pages are reused first (LIFO);
 * beside the pages, every request holds one slot of fixed-size state
   (the analogue of the reference's conv/ssm state, mamba_cache.py:63-70), even
@@ -104,10 +107,17 @@ class SlotPool:
 @dataclass(frozen=True)
 class GroupRule:
     """Lifetime rule of a group: ``window`` None keeps every page until the request ends; with a window, the
-    pages that hold any of the first ``keep_first`` positions are kept as well."""
+    pages that hold any of the first ``keep_first`` positions are kept as well. ``block`` (instead of a window):
+    queries see keys of their own block of that many positions only, and pages wholly before the block of the next
+    position are given back."""
 
     window: int | None
     keep_first: int = 0
+    block: int | None = None
+
+    def __post_init__(self) -> None:
+        if self.block is not None and (self.window is not None or self.block <= 0):
+            raise ValueError("a group's pages live by a window or by blocks of at least one position, not both")
 
 
 @dataclass
@@ -182,7 +192,9 @@ class CacheManager:
     # ------------------------------------------------------------------ pages
     def _first_needed_logical(self, group: int, length: int) -> int:
         """First logical page a query at position >= length can still see."""
-        window = self.rules[group].window
+        window, block = self.rules[group].window, self.rules[group].block
+        if block is not None:
+            return (length - length % block) // self.page_size
         if window is None:
             return 0
         return max(0, length - window + 1) // self.page_size

@@ -87,7 +87,8 @@ class EngineCore:
         pages_per_group = [pages for _ in plan.groups]
         self.model = model
         self.page_size = page_size
-        self.cache = CacheManager([GroupRule(window=g.request.window, keep_first=g.request.keep_first) for g in plan.groups],
+        self.cache = CacheManager([GroupRule(window=g.request.window, keep_first=g.request.keep_first, block=g.request.block)
+                                   for g in plan.groups],
                                   pages_per_group, page_size, max_requests)
         self.storage = CacheStorage(plan, pages_per_group, page_size, runtime.dtype,
                                     runtime.device, max_requests, poison=poison_cache)

@@ -146,6 +146,11 @@ class Scheduler:
                 # page is taken before the oldest is given back
                 kept = (self.cache.rules[group].keep_first + page_size - 1) // page_size
                 need = min(most_pages, (window - 1 + page_size - 1) // page_size + 2 + kept)
+            block = self.cache.rules[group].block
+            if block is not None:
+                # a block of B positions spans at most ceil((B - 1) / page) + 1 pages, and the next block's first
+                # page is taken before the old block's are given back
+                need = min(most_pages, (block - 1 + page_size - 1) // page_size + 2)
             if need > pool.num_pages:
                 raise RequestRefused(
                     f"request needs {need} pages in group {group}, the pool has {pool.num_pages}")

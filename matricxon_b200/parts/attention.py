@@ -570,9 +570,10 @@ class NormedRotaryAttention(Mixer):
 
     @classmethod
     def cache_request(cls, spec):
-        # blocks are kept whole (a later query of the same block needs them); only a window gives pages back
+        # pages live by the mask: a window's rule, or whole blocks until the sequence has left them
         return KVCacheRequest(num_kv_heads=spec.num_kv_heads, head_dim=cls.cache_head_dim(spec),
-                              window=spec.mask_size if spec.mask == "window" else None)
+                              window=spec.mask_size if spec.mask == "window" else None,
+                              block=spec.mask_size if spec.mask == "chunk" else None)
 
     def load(self, fetch):
         p, s = self.prefix, self.spec

@@ -87,13 +87,16 @@ class KVCacheRequest:
     the mixer's own business: the cache manager deals in pages, never in their contents.
     ``window`` None keeps every position; otherwise pages wholly older than the last
     ``window`` positions are given back, except those that hold any of the sequence's first
-    ``keep_first`` positions."""
+    ``keep_first`` positions. ``block`` (with ``window`` None): queries see the keys of their own block of
+    that many positions only (blocks counted from the sequence's start), and pages wholly before the block
+    of the next position are given back."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None
     planes: int = 2
     keep_first: int = 0
+    block: int | None = None
 
 
 @dataclass(frozen=True)

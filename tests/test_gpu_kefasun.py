@@ -267,9 +267,9 @@ def _paged_case(dtype, n_heads, n_kv, hd, page_size, contexts, q_lens, seed, spi
     tok_seq = torch.tensor([s for s in range(n_seqs) for _ in range(q_lens[s])], dtype=torch.int32)
     positions = torch.tensor([contexts[s] + i for s in range(n_seqs) for i in range(q_lens[s])], dtype=torch.int32)
     cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
-    meta = {"tables": tables.to(DEVICE), "tok_seq": tok_seq.to(DEVICE), "positions": positions.to(DEVICE),
+    meta = {"tables": tables, "tok_seq": tok_seq.to(DEVICE), "positions": positions.to(DEVICE),
             "cu_q": cu_q.to(DEVICE), "contexts": torch.tensor(contexts, dtype=torch.int32, device=DEVICE)}
-    return q.to(dtype).to(DEVICE), cache.to(dtype).to(DEVICE), meta, keys, values
+    return q.to(dtype).to(DEVICE), cache.to(dtype), meta, keys, values
 
 
 def _plain_attend(q, keys, values, contexts, q_lens, n_heads, n_kv, hd, scale, rule, size, sink):
@@ -294,7 +294,8 @@ def _plain_attend(q, keys, values, contexts, q_lens, n_heads, n_kv, hd, scale, r
     ("tc", torch.bfloat16, 128, 4), ("tc", torch.bfloat16, 128, 1)])
 @pytest.mark.parametrize("size", [44, 21, 16, 7, 64, 33, 150, 1, 128, 1000])
 def test_attention_kernels_over_blocks_of_positions(kernel, dtype, hd, group, size):
-    """Prompt portions and single tokens in one launch, shuffled pages, key splits, a sink of zero. The last query
+    """Prompt portions and single tokens in one launch, shuffled pages (those of blocks that the sequence has left
+    unmapped and poisoned), key splits, a sink of zero. The last query
     of every sequence meets a key equal to itself at the first position of its own block and at the last position
     of the block before: with a sharp scale each of them would take the softmax, and only the first may."""
     n_kv, n_heads, page = 2, 2 * group, 16
@@ -308,6 +309,15 @@ def test_attention_kernels_over_blocks_of_positions(kernel, dtype, hd, group, si
         spikes += [(s, j) for j in (start - 1, start) if 0 <= j < last]
     q, cache, meta, keys, values = _paged_case(dtype, n_heads, n_kv, hd, page, contexts, q_lens, seed=hd + group + size,
                                                spikes=spikes)
+    # what the cache manager would have given back before this step: pages wholly before the block of the step's
+    # first query; they are unmapped and poisoned
+    tables = meta["tables"].clone()
+    for s, c in enumerate(contexts):
+        for lp in range(min((c - c % size) // page, tables.shape[1])):
+            if tables[s, lp] >= 0:
+                cache[tables[s, lp]] = float("nan") if dtype == torch.float32 else 1e4
+                tables[s, lp] = -1
+    cache, meta["tables"] = cache.to(DEVICE), tables.to(DEVICE)
     scale = 12.0 / hd                                       # a key equal to the query scores 12, the others about 0
     n_tok = sum(q_lens)
     sink = torch.zeros(n_heads, dtype=torch.float32, device=DEVICE)

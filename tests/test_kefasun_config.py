@@ -59,7 +59,9 @@ def test_schedule_and_cache_plan():
     plan = plan_cache(spec)
     by_request = {(g.request.num_kv_heads, g.request.head_dim, g.request.window, g.request.planes): g.entries
                   for g in plan.groups}
-    assert by_request[(3, 48, None, 2)] == (0, 2, 4)              # every pass keeps a cache of its own; blocks keep every page
+    assert by_request[(3, 48, None, 2)] == (0, 2, 4)              # every pass keeps a cache of its own
+    assert [g.request.block for g in plan.groups if g.entries == (0, 2, 4)] == [11]      # pages live by blocks
+    assert [g.request.block for g in plan.groups if g.entries == (6,)] == [None]
     assert by_request[(1, 40, 9, 1)] == (1, 3, 5)                 # latent + rotated part, one plane, windowed
     assert by_request[(1, 48, None, 2)] == (6,)
     assert by_request[(1, 52, 37, 1)] == (7,)
@@ -68,6 +70,23 @@ def test_schedule_and_cache_plan():
     none = config_from_dict(copy.deepcopy(MODELS["C"])).model_spec()
     assert none.pass_input is None and [e.layer for e in none.schedule] == [0, 1, 2]
     assert [order for order in plain.layer_order(MODELS["A"])] == [(e.layer, e.pass_index) for e in spec.schedule]
+
+
+def test_pages_of_blocks_the_sequence_has_left_come_back():
+    from matricxon_b200.cache.manager import CacheManager, GroupRule
+
+    cache = CacheManager([GroupRule(window=None, block=10), GroupRule(window=None)], [12, 12], 4, 2)
+    cache.add_request("a")
+    for tokens, held in ((9, [0, 1, 2]), (1, [2]), (7, [2, 3, 4]), (3, []), (19, [7, 8, 9])):
+        cache.reserve("a", tokens)
+        cache.commit("a", tokens)
+        table = cache.record("a").tables[0]
+        # after `length` tokens the next query sits in the block of position `length`: earlier pages are gone
+        assert [lp for lp, page in enumerate(table) if page >= 0] == held, (cache.record("a").length, table)
+        assert all(page >= 0 for page in cache.record("a").tables[1])
+        cache.check_invariants()
+    with pytest.raises(ValueError):
+        GroupRule(window=5, block=5)
 
 
 def test_tensors_fill_in_ranks_and_note_what_lies_unused():
