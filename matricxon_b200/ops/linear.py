@@ -192,8 +192,9 @@ def batched_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
     if bias is None and kernels.batched_skinny_supported(x, weight, out):
         kernels.gemm_batched_skinny(x, weight, out)         # a decode step's few rows
         return out
-    if x.dtype == torch.bfloat16 and bias is None and x.shape[0] > 32:
-        # many rows: the library's strided batched product (float accumulator kept for a float result),
+    if x.dtype == torch.bfloat16 and bias is None and x.shape[0] > 16:
+        # more rows than the warp-per-column kernel takes (17 to 32 rows took 32 us a product on the FP32 cores at 16
+        # heads of 128 x 512): the library's strided batched product (float accumulator kept for a float result),
         # then one strided copy into the caller's interleaved layout
         acc = _bmm(x.transpose(0, 1), weight.transpose(1, 2), out.dtype)
         if acc is not None:
