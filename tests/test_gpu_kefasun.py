@@ -233,6 +233,29 @@ def test_norm_then_rotation_and_cache_write_kernel(dtype, interleaved, heads, kv
     assert float(host[pg, 0, 0, off, 0]) == 7.0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads, vdim, hd, offset", [(4, 64, 64, 8), (3, 24, 32, 4), (2, 128, 128, 6), (5, 40, 48, 0),
+                                                     (16, 128, 128, 1024)])
+def test_gate_kernels_per_entry_and_per_head(dtype, heads, vdim, hd, offset):
+    """The attention output (heads padded to hd) times sigmoid of a float gate that lies at a column offset of wider
+    rows: one gate per entry, or one per head; the padding is dropped."""
+    gen = torch.Generator().manual_seed(heads * vdim)
+    n = 37
+    attn = torch.randn(n, heads * hd, generator=gen).to(dtype)
+    wide = torch.randn(n, offset + heads * vdim + 3, generator=gen) * 3
+    values = attn.double().view(n, heads, hd)[:, :, :vdim]
+    out = torch.empty(n, heads * vdim, dtype=dtype, device=DEVICE)
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    gate = wide.to(DEVICE)[:, offset:offset + heads * vdim]
+    kernels.sigmoid_gate(attn.to(DEVICE), gate, out, heads, vdim)
+    want = values * torch.sigmoid(wide.double()[:, offset:offset + heads * vdim]).view(n, heads, vdim)
+    assert torch.allclose(out.double().cpu().view(n, heads, vdim), want, rtol=tol, atol=tol)
+    gate = wide.to(DEVICE)[:, offset:offset + heads]
+    kernels.head_gate(attn.to(DEVICE), gate, out, heads, vdim)
+    want = values * torch.sigmoid(wide.double()[:, offset:offset + heads])[:, :, None]
+    assert torch.allclose(out.double().cpu().view(n, heads, vdim), want, rtol=tol, atol=tol)
+
+
 def _paged_case(dtype, n_heads, n_kv, hd, page_size, contexts, q_lens, seed, spikes=()):
     """Queries and keys of unit root mean square in a paged cache with shuffled pages. ``spikes`` = (sequence, key
     position): that key equals the sequence's last query's first head of each group."""
